@@ -1,0 +1,422 @@
+#!/usr/bin/env python
+"""Benchmark of the grouped_mm forward hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Metric: useful TFLOP/s of the 2D x 3D MoE grouped_mm (Mixtral-shape up-projection: 8 experts,
+32768 routed rows, K=4096, N=14336, bf16 in/out, seeded multinomial-over-Dirichlet group sizes).
+One step = one forward call over one batch. Prints ONE JSON line on rank 0.
+
+  value     device-timed throughput with inputs resident in HBM (CUDA events, max over ranks)
+  e2e       the same metric through the public operator with HOST buffers: pinned host inputs are
+            copied to the device, the operator runs, the result is copied back, every step
+  roofline  tensor-core roofline of the one kernel a step launches
+  cpu_baseline  the CPU oracle (per-group fp32 torch.matmul) timed on a bounded sample
+  triton_reference  the reference package's own Triton kernel on the same inputs (rank 0, N=1)
+
+With N > 1 (torchrun, one rank per GPU) groups are sharded expert-parallel: every rank holds its
+own experts' weights and rows and runs the same per-GPU workload ("weak" scaling: the job has
+N x 8 experts and N x 32768 rows); no collective is inside the timed region. A "strong" split of
+the single 8-expert workload across ranks is timed afterwards and reported under
+`strong_scaling`, with the row imbalance of the split.
+
+`--impl reference` times the CPU restatement of the reference's path (the reference has no CPU
+compute path of its own) on the host cores, each step a bounded sample of the same workload.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+from grouped_mm_bf16_b200.workloads import (group_sizes, imbalance, make_workload, partition_groups)  # noqa: E402
+
+METRIC = "useful TFLOP/s, 2Dx3D MoE grouped_mm forward (Mixtral-shape)"
+UNIT = "TFLOP/s"
+
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of the tcgen05 kernel,
+# from an ncu capture; see profiles/. None until captured for that workload.
+NCU_TRAFFIC_BYTES = {}
+
+
+def read_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        d = json.loads(path.read_text())
+        return dict(tflops=float(d["bf16_tflops"]), tflops_sustained=float(d.get("bf16_tflops_sustained", 0) or 0),
+                    hbm_gbs=float(d["hbm_gbs"]), source="measured")
+    return dict(tflops=1590.0, tflops_sustained=1400.0, hbm_gbs=6650.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while a region runs."""
+
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
+
+    def __init__(self, index: int, period_s: float = 0.01):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        self._period = period_s
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            uuid = torch.cuda.get_device_properties(index).uuid
+            try:
+                self._h = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + str(uuid)).encode())
+            except Exception:
+                self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self._nv = None
+
+    def sample(self):
+        if self._nv is None:
+            return
+        try:
+            self.samples.append(int(self._nv.nvmlDeviceGetClockInfo(self._h, self._nv.NVML_CLOCK_SM)))
+            getter = getattr(self._nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                self._nv.nvmlDeviceGetCurrentClocksThrottleReasons
+            mask = int(getter(self._h))
+            for bit, name in self.REASONS.items():
+                if mask & bit:
+                    self.reasons.add(name)
+        except Exception:
+            pass
+
+    def _run(self):
+        while not self._stop.is_set():
+            self.sample()
+            time.sleep(self._period)
+
+    def __enter__(self):
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": 0}
+        return {"sm_mhz": int(statistics.median(self.samples)), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def dist_setup(n_gpus: int):
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        return dist, rank, world, local
+    torch.cuda.set_device(0)
+    return None, 0, 1, 0
+
+
+def barrier_sync(dist):
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(dist, value: float) -> float:
+    if dist is None:
+        return value
+    t = torch.tensor([value], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def sum_over_ranks(dist, value: float) -> float:
+    if dist is None:
+        return value
+    t = torch.tensor([value], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    return float(t.item())
+
+
+def time_steps(dist, step_fn, steps: int, warmup: int, sampler=None) -> float:
+    """Runs `warmup` untimed and exactly `steps` timed calls; returns ms for the timed region on
+    this rank (CUDA events on the launching stream, barrier + synchronize on both sides)."""
+    for _ in range(warmup):
+        step_fn()
+    barrier_sync(dist)
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ctx = sampler if sampler is not None else _Null()
+    with ctx:
+        start.record()
+        for _ in range(steps):
+            step_fn()
+        stop.record()
+        if sampler is not None:
+            sampler.sample()
+        barrier_sync(dist)
+    return start.elapsed_time(stop)
+
+
+class _Null:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
+def call_operator(wl):
+    from grouped_mm_bf16_b200 import grouped_mm
+
+    return grouped_mm(wl.mat_a, wl.mat_b, offs=wl.offs, out_dtype=wl.out_dtype)
+
+
+# ----------------------------------------------------------------------------- CPU baseline (oracle)
+
+
+def cpu_oracle_sample(a_cpu, b_cpu, sizes, budget_s: float):
+    """Per-group fp32 matmul on CPU tensors over a bounded prefix of every group's rows.
+
+    Returns (flops done, seconds, description). Rows are taken group by group in chunks until the
+    time budget is used, so the sample keeps the workload's K, N and group structure.
+    """
+    from oracle.grouped_mm_oracle import grouped_mm_oracle  # the checker, used here as the CPU baseline
+
+    k, n = a_cpu.size(1), b_cpu.size(2)
+    # calibrate on one 256-row slab of the first non-empty group
+    bounds, s = [], 0
+    for sz in sizes:
+        bounds.append((s, s + sz))
+        s += sz
+    g0 = next(g for g, (lo, hi) in enumerate(bounds) if hi > lo)
+    rows0 = min(256, bounds[g0][1] - bounds[g0][0])
+    t0 = time.perf_counter()
+    grouped_mm_oracle(a_cpu[bounds[g0][0]:bounds[g0][0] + rows0], b_cpu[g0:g0 + 1],
+                      torch.tensor([rows0], dtype=torch.int32))
+    per_row = max((time.perf_counter() - t0) / rows0, 1e-9)
+    live = [g for g, (lo, hi) in enumerate(bounds) if hi > lo]
+    rows_budget = max(len(live), int(budget_s / per_row))
+    take = {g: min(bounds[g][1] - bounds[g][0], max(1, rows_budget // len(live))) for g in live}
+    # build the sample as one smaller grouped problem
+    a_s = torch.cat([a_cpu[bounds[g][0]:bounds[g][0] + take[g]] for g in live])
+    offs_s = torch.tensor([take[g] for g in live], dtype=torch.int64).cumsum(0).to(torch.int32)
+    b_s = b_cpu[live]
+    t0 = time.perf_counter()
+    grouped_mm_oracle(a_s, b_s, offs_s)
+    dt = time.perf_counter() - t0
+    rows = int(a_s.size(0))
+    return 2.0 * rows * k * n, dt, f"first {rows} of {sum(sizes)} rows ({rows // len(live)} per group, {len(live)} groups), K={k}, N={n}"
+
+
+def run_reference_arm(args):
+    """`--impl reference`: the CPU restatement of the path on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    sizes = group_sizes(args.workload, 0)
+    wl = make_workload(args.workload, "cpu", seed=0, sizes=[min(s, 512) for s in sizes])
+    per_step = max(1.0, min(8.0, 150.0 / max(1, args.steps + args.warmup)))
+    times, flops, desc = [], 0.0, ""
+    for i in range(args.warmup + args.steps):
+        f, dt, desc = cpu_oracle_sample(wl.mat_a, wl.mat_b, wl.sizes, per_step)
+        if i >= args.warmup:
+            times.append(dt)
+            flops = f
+    ms = 1e3 * sum(times) / len(times)
+    value = flops / (ms * 1e-3) / 1e12
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "impl": "reference", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16 in, f32 accumulate", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: per-group fp32 torch.matmul on CPU, sample = {desc}"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------- Triton reference on the GPU
+
+
+def triton_reference_tflops(wl, steps: int, warmup: int):
+    """Times the unmodified reference package (installed under baseline/_ref) on the same inputs."""
+    import importlib.util
+
+    pkg = ROOT / "baseline" / "_ref" / "grouped_mm_bf16"
+    if not (pkg / "__init__.py").exists():
+        return {"unavailable": "baseline/_ref/grouped_mm_bf16 not present"}
+    try:
+        spec = importlib.util.spec_from_file_location("_reference_grouped_mm_bf16", pkg / "__init__.py",
+                                                      submodule_search_locations=[str(pkg)])
+        mod = importlib.util.module_from_spec(spec)
+        sys.modules["_reference_grouped_mm_bf16"] = mod
+        spec.loader.exec_module(mod)
+        fn = lambda: mod.grouped_mm(wl.mat_a, wl.mat_b, offs=wl.offs)  # noqa: E731
+        ms = time_steps(None, fn, steps, warmup) / steps
+        return {"value": wl.flops / (ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms, "steps": steps}
+    except Exception as exc:  # the baseline is informative; its failure must not hide our number
+        return {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
+
+
+# ----------------------------------------------------------------------------- main arm
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="mixtral",
+                    choices=["mixtral", "deepseek_up", "deepseek_down", "batched", "wgrad"])
+    ap.add_argument("--no-baselines", action="store_true", help="skip the CPU and Triton baseline legs")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    dist, rank, world, local = dist_setup(args.gpus)
+    dev = torch.device("cuda", local)
+    peaks = read_peaks()
+
+    # Every rank owns its own experts (weak scaling): same shape, its own seeded draw.
+    wl = make_workload(args.workload, dev, seed=rank)
+    from grouped_mm_bf16_b200 import _lib, _op
+
+    out = call_operator(wl)
+    form = {"2d3d": _lib.FORM_2D3D, "3d3d": _lib.FORM_3D3D, "2d2d": _lib.FORM_2D2D, "3d2d": _lib.FORM_3D2D}[wl.form]
+    kernel = _op.selected_kernel(form, wl.mat_a, wl.mat_b, out)
+    del out
+
+    sampler = ClockSampler(local)
+    ms_total = time_steps(dist, lambda: call_operator(wl), args.steps, args.warmup, sampler)
+    status = _op.check_status(dev)
+    ms_total = max_over_ranks(dist, ms_total)
+    ms_step = ms_total / args.steps
+    total_flops = sum_over_ranks(dist, wl.flops)
+    value = total_flops / (ms_step * 1e-3) / 1e12
+
+    # roofline of the one kernel a step launches (this rank's launch)
+    my_ms = ms_step
+    achieved = wl.flops / (my_ms * 1e-3) / 1e12
+    hbm_floor_ms = wl.algorithmic_bytes / (peaks["hbm_gbs"] * 1e9) * 1e3
+    tensor_floor_ms = wl.flops / (peaks["tflops"] * 1e12) * 1e3
+    if tensor_floor_ms >= hbm_floor_ms:
+        roofline = {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
+                    "frac": achieved / peaks["tflops"]}
+    else:
+        gbs = wl.algorithmic_bytes / (my_ms * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                    "frac": gbs / peaks["hbm_gbs"]}
+    roofline.update({
+        "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
+        "peak_source": f"{peaks['source']} (burst cuBLAS bf16 / copy bandwidth)",
+        "frac_of_sustained_peak": (achieved / peaks["tflops_sustained"]) if peaks["tflops_sustained"] else None,
+        "frac_of_nominal_2250": achieved / 2250.0,
+        "algorithmic_flops_per_launch": wl.flops, "algorithmic_bytes_per_launch": wl.algorithmic_bytes,
+        "kernel": {1: "gmm_sm100_kernel (TMA + tcgen05)", 2: "gmm_generic_kernel"}.get(kernel, "none"),
+    })
+
+    # end to end with host buffers
+    e2e = None
+    if not args.no_e2e:
+        a_h, b_h = wl.mat_a.cpu().pin_memory(), wl.mat_b.cpu().pin_memory()
+        offs_h = wl.offs.cpu().pin_memory() if wl.offs is not None else None
+        from grouped_mm_bf16_b200 import grouped_mm
+
+        probe = call_operator(wl)
+        out_h = torch.empty(probe.shape, dtype=probe.dtype).pin_memory()
+        del probe
+
+        def e2e_step():
+            a_d = a_h.to(dev, non_blocking=True)
+            b_d = b_h.to(dev, non_blocking=True)
+            o_d = offs_h.to(dev, non_blocking=True) if offs_h is not None else None
+            res = grouped_mm(a_d, b_d, offs=o_d, out_dtype=wl.out_dtype)
+            out_h.copy_(res, non_blocking=True)
+
+        e_steps = max(3, min(args.steps, 20))
+        e_ms = max_over_ranks(dist, time_steps(dist, e2e_step, e_steps, 3)) / e_steps
+        h2d = a_h.numel() * a_h.element_size() + b_h.numel() * b_h.element_size() + \
+            (offs_h.numel() * 4 if offs_h is not None else 0)
+        d2h = out_h.numel() * out_h.element_size()
+        e2e = {"value": total_flops / (e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": int(h2d),
+               "d2h_bytes_per_step": int(d2h), "ms_per_step": e_ms, "steps": e_steps}
+        del a_h, b_h, out_h
+
+    # strong split of ONE workload across the ranks (reported beside the weak number)
+    strong = None
+    if world > 1:
+        sizes = group_sizes(args.workload, 0)
+        if sizes is not None:
+            lo, hi = partition_groups(sizes, world)[rank]
+            local_sizes = sizes[lo:hi]
+            if sum(local_sizes) > 0:
+                swl = make_workload(args.workload, dev, seed=0, sizes=local_sizes)
+                s_ms = time_steps(dist, lambda: call_operator(swl), args.steps, args.warmup)
+                s_flops = swl.flops
+            else:
+                s_ms = time_steps(dist, lambda: None, args.steps, args.warmup)
+                s_flops = 0.0
+            s_ms_max = max_over_ranks(dist, s_ms) / args.steps
+            s_total = sum_over_ranks(dist, s_flops)
+            strong = {"value": s_total / (s_ms_max * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": s_ms_max,
+                      "row_balance_mean_over_max": imbalance(sizes, world),
+                      "note": "one 8-expert workload split by contiguous expert ranges, row-balanced"}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16 in/out, f32 accumulate", "data": "synthetic",
+            "config": {
+                "workload": f"{args.workload}: form {wl.form}, a {tuple(wl.mat_a.shape)}, b {tuple(wl.mat_b.shape)}, "
+                            f"{len(wl.sizes) if wl.sizes else wl.mat_a.size(0)} groups per GPU, seeded sizes",
+                "sharding": "expert-parallel, one process per GPU, no collective in the timed region",
+                "l2": "inputs larger than L2 (no flush needed)",
+            },
+            "roofline": roofline, "e2e": e2e, "gpu_launches": args.steps, "clocks": sampler.summary(),
+            "device_status": status,
+        }
+        if strong is not None:
+            line["strong_scaling"] = strong
+        if world == 1 and not args.no_baselines:
+            torch.set_num_threads(os.cpu_count() or 1)
+            f, dt, desc = cpu_oracle_sample(wl.mat_a.cpu(), wl.mat_b.cpu(), wl.sizes, 15.0) if wl.form == "2d3d" \
+                else (0.0, 1.0, "n/a")
+            line["cpu_baseline"] = {"value": f / dt / 1e12, "unit": UNIT, "cores": os.cpu_count() or 1,
+                                    "kind": "port", "sample": desc}
+            line["triton_reference"] = triton_reference_tflops(wl, max(3, min(args.steps, 20)), 3)
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

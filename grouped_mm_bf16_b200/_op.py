@@ -1,0 +1,134 @@
+"""The four kernel-level forward functions, bound to the C-ABI library.
+
+Mirrors the functions the reference's ``api.py`` imports from ``kernels.py``
+(grouped_mm_bf16/api.py:8-17; definitions kernels.py:524, 553, 583, 689): same names, same
+arguments, ``out`` pre-allocated by the caller and written in place, ``None`` returned, launch on
+the current CUDA stream without any host synchronisation. The work is registered as the torch
+custom op ``grouped_mm_b200::forward`` whose CUDA implementation passes raw pointers, sizes and
+strides to ``libgrouped_mm_b200.so`` through ctypes.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+_DTYPES = {torch.bfloat16: _lib.GMM_BF16, torch.float16: _lib.GMM_F16, torch.float32: _lib.GMM_F32}
+
+_ws_lock = threading.Lock()
+_workspaces: dict[int, torch.Tensor] = {}
+
+
+def workspace(device: torch.device) -> torch.Tensor:
+    """Per-device scratch (zero-filled once); its first int32 is the device status word."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    ws = _workspaces.get(idx)
+    if ws is None:
+        with _ws_lock:
+            ws = _workspaces.get(idx)
+            if ws is None:
+                nbytes = int(_lib.load().gmm_workspace_bytes())
+                ws = torch.zeros((nbytes + 3) // 4, dtype=torch.int32, device=torch.device("cuda", idx))
+                _workspaces[idx] = ws
+    return ws
+
+
+def _desc(t: torch.Tensor) -> _lib.GmmTensor:
+    d = _lib.GmmTensor()
+    d.data = t.data_ptr()
+    d.dtype = _DTYPES[t.dtype]
+    d.ndim = t.dim()
+    for i in range(t.dim()):
+        d.size[i] = t.size(i)
+        d.stride[i] = t.stride(i)
+    return d
+
+
+def _flags() -> int:
+    return _lib.GMM_FLAG_FORCE_GENERIC if os.environ.get("GROUPED_MM_B200_FORCE_GENERIC", "0") == "1" else 0
+
+
+def _launch(form: int, mat_a: torch.Tensor, mat_b: torch.Tensor, offs: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    lib = _lib.load()
+    if not (mat_a.is_cuda and mat_b.is_cuda and out.is_cuda):
+        raise RuntimeError("grouped_mm_b200 is GPU-only; CPU tensors are not supported")
+    dev = mat_a.device
+    with torch.cuda.device(dev):
+        ws = workspace(dev)
+        launch = _lib.GmmLaunch()
+        launch.stream = torch.cuda.current_stream(dev).cuda_stream
+        launch.workspace = ws.data_ptr()
+        launch.workspace_bytes = ws.numel() * 4
+        launch.flags = _flags()
+        a, b, c = _desc(mat_a), _desc(mat_b), _desc(out)
+        if form == _lib.FORM_3D3D:
+            rc = lib.grouped_mm_3d3d(ctypes.byref(a), ctypes.byref(b), ctypes.byref(c), ctypes.byref(launch))
+        else:
+            fn = {_lib.FORM_2D3D: lib.grouped_mm_2d3d, _lib.FORM_3D2D: lib.grouped_mm_3d2d,
+                  _lib.FORM_2D2D: lib.grouped_mm_2d2d}[form]
+            rc = fn(ctypes.byref(a), ctypes.byref(b), ctypes.c_void_p(offs.data_ptr()), int(offs.numel()),
+                    ctypes.byref(c), ctypes.byref(launch))
+    if rc != 0:
+        raise RuntimeError(_lib.error_message(lib, rc))
+
+
+@torch.library.custom_op("grouped_mm_b200::forward", mutates_args=("out",), device_types="cuda")
+def _forward_op(mat_a: torch.Tensor, mat_b: torch.Tensor, offs: Optional[torch.Tensor], out: torch.Tensor,
+                form: int) -> None:
+    _launch(form, mat_a, mat_b, offs, out)
+
+
+@_forward_op.register_fake
+def _(mat_a, mat_b, offs, out, form):
+    return None
+
+
+def grouped_mm_3d3d(mat_a: torch.Tensor, mat_b: torch.Tensor, out: torch.Tensor) -> None:
+    """out[g] = mat_a[g] @ mat_b[g] (reference: kernels.py:524-550)."""
+    _forward_op(mat_a, mat_b, None, out, _lib.FORM_3D3D)
+
+
+def grouped_mm_2d2d(mat_a: torch.Tensor, mat_b: torch.Tensor, offs: torch.Tensor, out: torch.Tensor) -> None:
+    """out[g] = mat_a[:, ks:ke] @ mat_b[ks:ke, :], zeros for an empty range (reference: kernels.py:553-580)."""
+    _forward_op(mat_a, mat_b, offs, out, _lib.FORM_2D2D)
+
+
+def grouped_mm_2d3d(mat_a: torch.Tensor, mat_b: torch.Tensor, offs: torch.Tensor, out: torch.Tensor) -> None:
+    """out[rows_g] = mat_a[rows_g] @ mat_b[g] (reference: kernels.py:583-686)."""
+    _forward_op(mat_a, mat_b, offs, out, _lib.FORM_2D3D)
+
+
+def grouped_mm_3d2d(mat_a: torch.Tensor, mat_b: torch.Tensor, offs: torch.Tensor, out: torch.Tensor) -> None:
+    """out[:, cols_g] = mat_a[g] @ mat_b[:, cols_g] (reference: kernels.py:689-717)."""
+    if mat_a.size(0) != offs.numel():
+        raise RuntimeError("matrix batch sizes have to match")
+    _forward_op(mat_a, mat_b, offs, out, _lib.FORM_3D2D)
+
+
+def selected_kernel(form: int, mat_a: torch.Tensor, mat_b: torch.Tensor, out: torch.Tensor) -> int:
+    """Which kernel a call with these tensors is routed to (0 none, 1 tcgen05, 2 generic)."""
+    lib = _lib.load()
+    a, b, c = _desc(mat_a), _desc(mat_b), _desc(out)
+    rc = lib.gmm_select_kernel(form, ctypes.byref(a), ctypes.byref(b), ctypes.byref(c), _flags())
+    if rc < 0:
+        raise RuntimeError(_lib.error_message(lib, rc))
+    return rc
+
+
+def check_status(device: torch.device) -> int:
+    """Synchronises the current stream and returns the device status word (0 = no wait gave up)."""
+    lib = _lib.load()
+    with torch.cuda.device(device):
+        ws = workspace(device)
+        raw = ctypes.c_int32(0)
+        rc = lib.gmm_check_status(ctypes.c_void_p(ws.data_ptr()),
+                                  ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream), ctypes.byref(raw))
+    if rc not in (0, _lib.GMM_ERR_DEVICE_WAIT):
+        raise RuntimeError(_lib.error_message(lib, rc))
+    return int(raw.value)

@@ -1,0 +1,439 @@
+// Host side of libgrouped_mm_b200.so: argument checking, reduction of the four shape forms to
+// the three canonical modes, kernel selection, tensor-map encoding and launch. Declared in
+// include/grouped_mm_b200.h. Nothing here allocates device memory or waits for the device
+// (gmm_check_status excepted, which exists to wait).
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <mutex>
+#include <string>
+
+#include "../../include/grouped_mm_b200.h"
+#include "gmm_common.cuh"
+#include "gmm_generic_kernel.cuh"
+#include "gmm_sm100_kernel.cuh"
+
+namespace {
+
+using namespace gmm;
+
+thread_local std::string g_last_cuda_error;
+
+int cuda_fail(cudaError_t e, const char* what) {
+  g_last_cuda_error = std::string(what) + ": " + cudaGetErrorString(e);
+  return GMM_ERR_CUDA;
+}
+
+#define GMM_CUDA_TRY(expr)                               \
+  do {                                                   \
+    cudaError_t e__ = (expr);                            \
+    if (e__ != cudaSuccess) return cuda_fail(e__, #expr); \
+  } while (0)
+
+// ------------------------------------------------------------------ per-device facts
+
+constexpr int kMaxDevices = 64;
+struct DeviceInfo {
+  std::once_flag once;
+  int status = GMM_OK;
+  int sm_count = 0;
+  int cc_major = 0;
+};
+DeviceInfo g_dev[kMaxDevices];
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+std::once_flag g_encode_once;
+EncodeTiledFn g_encode = nullptr;
+
+EncodeTiledFn get_encode() {
+  std::call_once(g_encode_once, [] {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+  });
+  return g_encode;
+}
+
+template <typename K>
+int set_smem_attr(K kernel) {
+  GMM_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFastSmemBytes));
+  return GMM_OK;
+}
+
+int init_device(int dev) {
+  DeviceInfo& d = g_dev[dev];
+  std::call_once(d.once, [&] {
+    cudaError_t e = cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev);
+    if (e != cudaSuccess) { d.status = cuda_fail(e, "cudaDeviceGetAttribute"); return; }
+    if (d.cc_major != 10) { d.status = GMM_ERR_NOT_SM100; return; }
+    int rc = GMM_OK;
+    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_kernel<false, __nv_bfloat16>);
+    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_kernel<false, __half>);
+    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_kernel<false, float>);
+    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_kernel<true, __nv_bfloat16>);
+    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_kernel<true, __half>);
+    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_kernel<true, float>);
+    d.status = rc;
+  });
+  return d.status;
+}
+
+// ------------------------------------------------------------------ canonicalisation
+
+bool tensor_ok(const gmm_tensor_t* t, int ndim) {
+  if (!t || t->ndim != ndim) return false;
+  if (t->dtype < GMM_BF16 || t->dtype > GMM_F32) return false;
+  for (int i = 0; i < ndim; ++i)
+    if (t->size[i] < 0 || t->size[i] > 0x7fffffffLL) return false;
+  return true;
+}
+
+long long numel(const gmm_tensor_t* t) {
+  long long n = 1;
+  for (int i = 0; i < t->ndim; ++i) n *= t->size[i];
+  return n;
+}
+
+// form: 0 = 3d3d, 1 = 2d3d, 2 = 3d2d, 3 = 2d2d. On success *nothing is set when the call has no
+// work (empty output or no groups).
+int canonicalise(int form, const gmm_tensor_t* a, const gmm_tensor_t* b, const int32_t* offs, int n_groups,
+                 const gmm_tensor_t* out, CanonProblem* cp, bool* nothing, bool need_pointers) {
+  *nothing = false;
+  const int a_nd = (form == 0 || form == 2) ? 3 : 2;
+  const int b_nd = (form == 0 || form == 1) ? 3 : 2;
+  const int c_nd = (form == 0 || form == 3) ? 3 : 2;
+  if (form < 0 || form > 3) return GMM_ERR_INVALID_ARGUMENT;
+  if (!tensor_ok(a, a_nd) || !tensor_ok(b, b_nd) || !tensor_ok(out, c_nd)) {
+    if (a && b && out && (a->dtype < GMM_BF16 || a->dtype > GMM_F32 || b->dtype < GMM_BF16 ||
+                          b->dtype > GMM_F32 || out->dtype < GMM_BF16 || out->dtype > GMM_F32))
+      return GMM_ERR_UNSUPPORTED_DTYPE;
+    return GMM_ERR_INVALID_ARGUMENT;
+  }
+  if (a->dtype != b->dtype) return GMM_ERR_INVALID_ARGUMENT;
+  if (form != 0) {
+    if (n_groups < 0) return GMM_ERR_INVALID_ARGUMENT;
+    if (n_groups >= kMaxGroups) return GMM_ERR_TOO_MANY_GROUPS;
+    if (need_pointers && n_groups > 0 && !offs) return GMM_ERR_INVALID_ARGUMENT;
+  }
+
+  CanonProblem p = {};
+  p.a = a->data;
+  p.b = b->data;
+  p.c = out->data;
+  p.offs = offs;
+  p.in_dtype = a->dtype;
+  p.out_dtype = out->dtype;
+  switch (form) {
+    case 0: {  // [G,M,K] x [G,K,N] -> [G,M,N]
+      if (a->size[0] != b->size[0] || a->size[2] != b->size[1]) return GMM_ERR_INVALID_ARGUMENT;
+      if (out->size[0] != a->size[0] || out->size[1] != a->size[1] || out->size[2] != b->size[2])
+        return GMM_ERR_INVALID_ARGUMENT;
+      p.mode = MODE_UNIFORM;
+      p.G = (int)a->size[0]; p.M = (int)a->size[1]; p.K = (int)a->size[2]; p.N = (int)b->size[2];
+      p.a_sg = a->stride[0]; p.a_sm = a->stride[1]; p.a_sk = a->stride[2];
+      p.b_sg = b->stride[0]; p.b_sk = b->stride[1]; p.b_sn = b->stride[2];
+      p.c_sg = out->stride[0]; p.c_sm = out->stride[1]; p.c_sn = out->stride[2];
+      p.offs = nullptr;
+      break;
+    }
+    case 1: {  // [Mt,K] x [G,K,N] -> [Mt,N]
+      if (a->size[1] != b->size[1] || b->size[0] != n_groups) return GMM_ERR_INVALID_ARGUMENT;
+      if (out->size[0] != a->size[0] || out->size[1] != b->size[2]) return GMM_ERR_INVALID_ARGUMENT;
+      p.mode = MODE_MRAGGED;
+      p.G = n_groups; p.M = (int)a->size[0]; p.K = (int)a->size[1]; p.N = (int)b->size[2];
+      p.a_sg = 0; p.a_sm = a->stride[0]; p.a_sk = a->stride[1];
+      p.b_sg = b->stride[0]; p.b_sk = b->stride[1]; p.b_sn = b->stride[2];
+      p.c_sg = 0; p.c_sm = out->stride[0]; p.c_sn = out->stride[1];
+      break;
+    }
+    case 2: {  // [G,M,K] x [K,Nt] -> [M,Nt], computed as out^T = b^T * a[g]^T (row-ragged)
+      if (a->size[2] != b->size[0] || a->size[0] != n_groups) return GMM_ERR_INVALID_ARGUMENT;
+      if (out->size[0] != a->size[1] || out->size[1] != b->size[1]) return GMM_ERR_INVALID_ARGUMENT;
+      p.mode = MODE_MRAGGED;
+      p.G = n_groups; p.M = (int)b->size[1]; p.K = (int)a->size[2]; p.N = (int)a->size[1];
+      p.a = b->data; p.b = a->data;
+      p.a_sg = 0; p.a_sm = b->stride[1]; p.a_sk = b->stride[0];
+      p.b_sg = a->stride[0]; p.b_sk = a->stride[2]; p.b_sn = a->stride[1];
+      p.c_sg = 0; p.c_sm = out->stride[1]; p.c_sn = out->stride[0];
+      break;
+    }
+    default: {  // [M,Kt] x [Kt,N] -> [G,M,N]
+      if (a->size[1] != b->size[0]) return GMM_ERR_INVALID_ARGUMENT;
+      if (out->size[0] != n_groups || out->size[1] != a->size[0] || out->size[2] != b->size[1])
+        return GMM_ERR_INVALID_ARGUMENT;
+      p.mode = MODE_KRAGGED;
+      p.G = n_groups; p.M = (int)a->size[0]; p.K = (int)a->size[1]; p.N = (int)b->size[1];
+      p.a_sg = 0; p.a_sm = a->stride[0]; p.a_sk = a->stride[1];
+      p.b_sg = 0; p.b_sk = b->stride[0]; p.b_sn = b->stride[1];
+      p.c_sg = out->stride[0]; p.c_sm = out->stride[1]; p.c_sn = out->stride[2];
+      break;
+    }
+  }
+  if (numel(out) == 0 || p.G == 0) { *nothing = true; *cp = p; return GMM_OK; }
+  if (need_pointers) {
+    if (!p.c) return GMM_ERR_INVALID_ARGUMENT;
+    if (p.K > 0 && (!p.a || !p.b)) return GMM_ERR_INVALID_ARGUMENT;
+  }
+  *cp = p;
+  return GMM_OK;
+}
+
+// ------------------------------------------------------------------ kernel selection
+
+struct FastPlan {
+  bool ok = false;
+  int a_mn = 0;
+  int b_mn = 0;
+};
+
+bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; }
+
+// The TMA path needs 16-bit inputs, 16-byte aligned bases and leading/group strides, and the
+// ragged dimension must not be the contiguous one (a group may start at any index of it, while a
+// TMA box must start on a 16-byte boundary of the contiguous dimension).
+FastPlan plan_fast(const CanonProblem& p) {
+  FastPlan f;
+  if (p.in_dtype == DT_F32 || p.K < 1) return f;
+  if (!aligned16(p.a) || !aligned16(p.b)) return f;
+  if (p.a_sk == 1 && p.a_sm % 8 == 0 && p.a_sm >= p.K) f.a_mn = 0;
+  else if (p.a_sm == 1 && p.a_sk % 8 == 0 && p.a_sk >= p.M) f.a_mn = 1;
+  else return f;
+  if (p.b_sk == 1 && p.b_sn % 8 == 0 && p.b_sn >= p.K) f.b_mn = 0;
+  else if (p.b_sn == 1 && p.b_sk % 8 == 0 && p.b_sk >= p.N) f.b_mn = 1;
+  else return f;
+  if (p.mode == MODE_UNIFORM && p.G > 1 && (p.a_sg <= 0 || p.a_sg % 8 != 0)) return f;
+  if (p.mode != MODE_KRAGGED && p.G > 1 && (p.b_sg <= 0 || p.b_sg % 8 != 0)) return f;
+  if (p.mode == MODE_MRAGGED && f.a_mn) return f;
+  if (p.mode == MODE_KRAGGED && !(f.a_mn && f.b_mn)) return f;
+  f.ok = true;
+  return f;
+}
+
+// ------------------------------------------------------------------ tensor maps
+
+// 3-D map (inner, outer, batch) over a 16-bit operand with a 128-byte-swizzled box.
+int encode_map(CUtensorMap* map, const void* base, int in_dtype, long long inner, long long outer,
+               long long batch, long long outer_stride_elems, long long batch_stride_elems, int box_outer) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) {
+    g_last_cuda_error = "cuTensorMapEncodeTiled entry point not found";
+    return GMM_ERR_CUDA;
+  }
+  cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)outer, (cuuint64_t)(batch > 0 ? batch : 1)};
+  if (batch <= 1) batch_stride_elems = outer_stride_elems * outer;
+  cuuint64_t strides[2] = {(cuuint64_t)outer_stride_elems * 2, (cuuint64_t)batch_stride_elems * 2};
+  cuuint32_t box[3] = {64, (cuuint32_t)box_outer, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(map, in_dtype == DT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                   const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    g_last_cuda_error = "cuTensorMapEncodeTiled failed with CUresult " + std::to_string((int)r);
+    return GMM_ERR_CUDA;
+  }
+  return GMM_OK;
+}
+
+uint32_t make_idesc(int in_dtype, int a_mn, int b_mn) {
+  const uint32_t fmt = (in_dtype == DT_BF16) ? 1u : 0u;  // 0 = f16, 1 = bf16
+  uint32_t d = 0;
+  d |= 1u << 4;                        // accumulator format: f32
+  d |= fmt << 7;                       // A format
+  d |= fmt << 10;                      // B format
+  d |= (uint32_t)(a_mn ? 1 : 0) << 15; // A major: 0 = K, 1 = MN
+  d |= (uint32_t)(b_mn ? 1 : 0) << 16; // B major
+  d |= (uint32_t)(kBN >> 3) << 17;     // N / 8
+  d |= (uint32_t)(kBM >> 4) << 24;     // M / 16
+  return d;
+}
+
+// ------------------------------------------------------------------ launches
+
+template <typename TIn>
+int launch_generic_in(const CanonProblem& p, int grid, cudaStream_t st) {
+  switch (p.out_dtype) {
+    case DT_BF16: gmm_generic_kernel<TIn, __nv_bfloat16><<<grid, kGenericThreads, 0, st>>>(p); break;
+    case DT_F16: gmm_generic_kernel<TIn, __half><<<grid, kGenericThreads, 0, st>>>(p); break;
+    default: gmm_generic_kernel<TIn, float><<<grid, kGenericThreads, 0, st>>>(p); break;
+  }
+  GMM_CUDA_TRY(cudaGetLastError());
+  return GMM_OK;
+}
+
+long long tile_upper_bound(const CanonProblem& p, int bm, int bn) {
+  const long long nt = (p.N + bn - 1) / bn;
+  long long mt;
+  if (p.mode == MODE_MRAGGED) mt = (p.M + bm - 1) / bm + p.G;  // at most one partial tile more per group
+  else mt = (long long)p.G * ((p.M + bm - 1) / bm);
+  return mt * nt;
+}
+
+int launch_generic(const CanonProblem& p, const DeviceInfo& d, cudaStream_t st) {
+  const long long ub = tile_upper_bound(p, kGBM, kGBN);
+  if (ub <= 0) return GMM_OK;
+  if (ub > 0x7fffffffLL) return GMM_ERR_INVALID_ARGUMENT;
+  const long long cap = (long long)d.sm_count * 8;
+  const int grid = (int)(ub < cap ? ub : cap);
+  switch (p.in_dtype) {
+    case DT_BF16: return launch_generic_in<__nv_bfloat16>(p, grid, st);
+    case DT_F16: return launch_generic_in<__half>(p, grid, st);
+    default: return launch_generic_in<float>(p, grid, st);
+  }
+}
+
+template <bool KR>
+int launch_fast_kr(const CUtensorMap& ta, const CUtensorMap& tb, const FastParams& fp, int grid, cudaStream_t st) {
+  switch (fp.p.out_dtype) {
+    case DT_BF16:
+      gmm_sm100_kernel<KR, __nv_bfloat16><<<grid, kFastThreads, kFastSmemBytes, st>>>(ta, tb, fp);
+      break;
+    case DT_F16:
+      gmm_sm100_kernel<KR, __half><<<grid, kFastThreads, kFastSmemBytes, st>>>(ta, tb, fp);
+      break;
+    default:
+      gmm_sm100_kernel<KR, float><<<grid, kFastThreads, kFastSmemBytes, st>>>(ta, tb, fp);
+      break;
+  }
+  GMM_CUDA_TRY(cudaGetLastError());
+  return GMM_OK;
+}
+
+int launch_fast(const CanonProblem& p, const FastPlan& plan, const DeviceInfo& d, cudaStream_t st) {
+  const long long ub = tile_upper_bound(p, kBM, kBN);
+  if (ub <= 0) return GMM_OK;
+  if (ub > 0x7fffffffLL) return GMM_ERR_INVALID_ARGUMENT;
+  const int grid = (int)(ub < d.sm_count ? ub : d.sm_count);
+
+  const bool a_batched = (p.mode == MODE_UNIFORM);
+  const bool b_batched = (p.mode != MODE_KRAGGED);
+  CUtensorMap ta, tb;
+  int rc;
+  if (!plan.a_mn)
+    rc = encode_map(&ta, p.a, p.in_dtype, p.K, p.M, a_batched ? p.G : 1, p.a_sm, p.a_sg, kBM);
+  else
+    rc = encode_map(&ta, p.a, p.in_dtype, p.M, p.K, a_batched ? p.G : 1, p.a_sk, p.a_sg, kBK);
+  if (rc != GMM_OK) return rc;
+  if (!plan.b_mn)
+    rc = encode_map(&tb, p.b, p.in_dtype, p.K, p.N, b_batched ? p.G : 1, p.b_sn, p.b_sg, kBN);
+  else
+    rc = encode_map(&tb, p.b, p.in_dtype, p.N, p.K, b_batched ? p.G : 1, p.b_sk, p.b_sg, kBK);
+  if (rc != GMM_OK) return rc;
+
+  FastParams fp;
+  fp.p = p;
+  fp.a_mn = plan.a_mn;
+  fp.b_mn = plan.b_mn;
+  fp.idesc = make_idesc(p.in_dtype, plan.a_mn, plan.b_mn);
+  return p.mode == MODE_KRAGGED ? launch_fast_kr<true>(ta, tb, fp, grid, st)
+                                : launch_fast_kr<false>(ta, tb, fp, grid, st);
+}
+
+constexpr size_t kWorkspaceBytes = 256;
+
+int run(int form, const gmm_tensor_t* a, const gmm_tensor_t* b, const int32_t* offs, int n_groups,
+        const gmm_tensor_t* out, const gmm_launch_t* launch) {
+  if (!launch) return GMM_ERR_INVALID_ARGUMENT;
+  CanonProblem p;
+  bool nothing;
+  int rc = canonicalise(form, a, b, offs, n_groups, out, &p, &nothing, true);
+  if (rc != GMM_OK) return rc;
+  if (nothing) return GMM_OK;
+  if (!launch->workspace || launch->workspace_bytes < kWorkspaceBytes ||
+      (reinterpret_cast<uintptr_t>(launch->workspace) & 255u))
+    return GMM_ERR_WORKSPACE;
+  p.status = reinterpret_cast<int*>(launch->workspace);
+
+  int dev = 0;
+  GMM_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return GMM_ERR_INVALID_ARGUMENT;
+  rc = init_device(dev);
+  if (rc != GMM_OK) return rc;
+  const DeviceInfo& d = g_dev[dev];
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(launch->stream);
+
+  const FastPlan plan = (launch->flags & GMM_FLAG_FORCE_GENERIC) ? FastPlan() : plan_fast(p);
+  return plan.ok ? launch_fast(p, plan, d, st) : launch_generic(p, d, st);
+}
+
+}  // namespace
+
+// ====================================================================== C ABI
+
+extern "C" {
+
+int gmm_abi_version(void) { return GMM_ABI_VERSION; }
+
+const char* gmm_error_string(int status) {
+  switch (status) {
+    case GMM_OK: return "ok";
+    case GMM_ERR_INVALID_ARGUMENT: return "invalid argument (null pointer, rank, size or shape mismatch)";
+    case GMM_ERR_UNSUPPORTED_DTYPE: return "unsupported dtype (expected bf16, fp16 or fp32)";
+    case GMM_ERR_TOO_MANY_GROUPS: return "Can't process more than 1024 groups";
+    case GMM_ERR_WORKSPACE: return "workspace missing, misaligned or too small";
+    case GMM_ERR_CUDA: return "CUDA call failed";
+    case GMM_ERR_NOT_SM100: return "device is not compute capability 10.x (B200)";
+    case GMM_ERR_DEVICE_WAIT: return "a bounded wait inside the kernel gave up; outputs are invalid";
+    default: return "unknown status";
+  }
+}
+
+const char* gmm_last_cuda_error(void) { return g_last_cuda_error.c_str(); }
+
+size_t gmm_workspace_bytes(void) { return kWorkspaceBytes; }
+
+int grouped_mm_3d3d(const gmm_tensor_t* a, const gmm_tensor_t* b, const gmm_tensor_t* out,
+                    const gmm_launch_t* launch) {
+  return run(0, a, b, nullptr, 0, out, launch);
+}
+
+int grouped_mm_2d3d(const gmm_tensor_t* a, const gmm_tensor_t* b, const int32_t* offs, int32_t n_groups,
+                    const gmm_tensor_t* out, const gmm_launch_t* launch) {
+  return run(1, a, b, offs, n_groups, out, launch);
+}
+
+int grouped_mm_3d2d(const gmm_tensor_t* a, const gmm_tensor_t* b, const int32_t* offs, int32_t n_groups,
+                    const gmm_tensor_t* out, const gmm_launch_t* launch) {
+  return run(2, a, b, offs, n_groups, out, launch);
+}
+
+int grouped_mm_2d2d(const gmm_tensor_t* a, const gmm_tensor_t* b, const int32_t* offs, int32_t n_groups,
+                    const gmm_tensor_t* out, const gmm_launch_t* launch) {
+  return run(3, a, b, offs, n_groups, out, launch);
+}
+
+int gmm_select_kernel(int32_t form, const gmm_tensor_t* a, const gmm_tensor_t* b, const gmm_tensor_t* out,
+                      uint32_t flags) {
+  CanonProblem p;
+  bool nothing;
+  int n_groups = 0;
+  if (form == 1 && b) n_groups = (int)b->size[0];
+  if (form == 2 && a) n_groups = (int)a->size[0];
+  if (form == 3 && out) n_groups = (int)out->size[0];
+  int rc = canonicalise(form, a, b, nullptr, n_groups, out, &p, &nothing, false);
+  if (rc != GMM_OK) return rc;
+  if (nothing) return GMM_KERNEL_NONE;
+  if (flags & GMM_FLAG_FORCE_GENERIC) return GMM_KERNEL_GENERIC;
+  return plan_fast(p).ok ? GMM_KERNEL_TCGEN05 : GMM_KERNEL_GENERIC;
+}
+
+int gmm_check_status(void* workspace, void* stream, int32_t* raw) {
+  if (!workspace) return GMM_ERR_WORKSPACE;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  GMM_CUDA_TRY(cudaStreamSynchronize(st));
+  int32_t v = 0;
+  GMM_CUDA_TRY(cudaMemcpy(&v, workspace, sizeof(v), cudaMemcpyDeviceToHost));
+  if (raw) *raw = v;
+  if (v != 0) {
+    GMM_CUDA_TRY(cudaMemset(workspace, 0, sizeof(v)));
+    return GMM_ERR_DEVICE_WAIT;
+  }
+  return GMM_OK;
+}
+
+}  // extern "C"

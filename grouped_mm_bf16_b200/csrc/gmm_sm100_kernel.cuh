@@ -1,0 +1,331 @@
+// Persistent, warp-specialised grouped GEMM for sm_100a.
+//
+//   warp 0      TMA producer   : cp.async.bulk.tensor loads of A/B k-blocks into a 4-stage ring
+//   warp 1      MMA issuer     : tcgen05.mma (128 x 256 x 16, bf16/fp16 in, fp32 accumulate in TMEM)
+//   warps 2..5  epilogue       : tcgen05.ld -> one rounding to the output type -> masked global stores
+//
+// Each CTA owns 512 TMEM columns = two 128 x 256 fp32 accumulators, so the epilogue of tile i
+// overlaps the main loop of tile i+1. Tiles are (group, m-tile, n-tile) items decoded on the
+// device from `offs` (gmm_common.cuh); every role walks the same sequence
+// blockIdx.x, blockIdx.x + gridDim.x, ...
+//
+// Replaces the reference's Triton kernels for the same math: kernels.py:197-245 (3D x 3D),
+// kernels.py:304-419 (2D x 3D main + prologue pair) and kernels.py:248-301 (2D x 2D), all of
+// which accumulate in fp32 and round once at the store, as this kernel does.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "gmm_common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace gmm {
+
+constexpr int kBM = 128;
+constexpr int kBN = 256;
+constexpr int kBK = 64;   // 64 16-bit elements = one 128-byte swizzle row
+constexpr int kUmmaK = 16;
+constexpr int kStages = 4;
+constexpr int kAStageBytes = kBM * kBK * 2;          // 16 KiB
+constexpr int kBStageBytes = kBN * kBK * 2;          // 32 KiB
+constexpr int kStageBytes = kAStageBytes + kBStageBytes;
+constexpr int kChunkBytes = 64 * kBK * 2;            // one 64-wide MN chunk of an MN-major operand: 8 KiB
+constexpr int kTmemCols = 512;
+constexpr int kFastThreads = 192;
+constexpr int kEpilogueThreads = 128;
+
+struct FastSmemTail {
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+  SchedSmem sched;
+};
+
+constexpr size_t kFastSmemBytes = 1024 /*alignment slack*/ + size_t(kStages) * kStageBytes + sizeof(FastSmemTail);
+
+struct FastParams {
+  CanonProblem p;
+  uint32_t idesc;  // tcgen05 instruction descriptor (formats, majors, M=128, N=256)
+  int a_mn;        // 1: A is MN-major in memory (column-major [M,K]); 0: K-major
+  int b_mn;        // 1: B is MN-major in memory (row-major [K,N]);    0: K-major
+};
+
+// Status codes written to CanonProblem::status when a bounded wait gives up.
+enum FastStatus : int {
+  ST_OK = 0,
+  ST_PRODUCER_TIMEOUT = 0x101,
+  ST_MMA_TIMEOUT = 0x102,
+  ST_EPILOGUE_TIMEOUT = 0x103,
+};
+
+template <typename TOut>
+struct OutCvt;
+template <>
+struct OutCvt<__nv_bfloat16> {
+  static __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+  static __device__ __forceinline__ __nv_bfloat16 one(float x) { return __float2bfloat16_rn(x); }
+};
+template <>
+struct OutCvt<__half> {
+  static __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+  static __device__ __forceinline__ __half one(float x) { return __float2half_rn(x); }
+};
+template <>
+struct OutCvt<float> {
+  static __device__ __forceinline__ float one(float x) { return x; }
+};
+
+// Stores up to 32 consecutive columns of one output row. `r` holds fp32 bit patterns.
+template <typename TOut>
+__device__ __forceinline__ void store_row_chunk(TOut* dst, long long col_stride, const uint32_t (&r)[32],
+                                                int ncols) {
+  const bool vec = (col_stride == 1) && (ncols == 32) && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0);
+  if (vec) {
+    if constexpr (sizeof(TOut) == 4) {
+      uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) d4[i] = make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+    } else {
+      uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        uint4 v;
+        v.x = OutCvt<TOut>::pack2(__uint_as_float(r[8 * i + 0]), __uint_as_float(r[8 * i + 1]));
+        v.y = OutCvt<TOut>::pack2(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
+        v.z = OutCvt<TOut>::pack2(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
+        v.w = OutCvt<TOut>::pack2(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
+        d4[i] = v;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      if (i < ncols) dst[i * col_stride] = OutCvt<TOut>::one(__uint_as_float(r[i]));
+    }
+  }
+}
+
+template <bool KRAGGED, typename TOut>
+__global__ void __launch_bounds__(kFastThreads, 1)
+gmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const FastParams fp) {
+  extern __shared__ uint8_t smem_raw[];
+  // 128-byte swizzled tiles must start on 1024-byte boundaries.
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_a = smem;
+  uint8_t* smem_b = smem + kStages * kAStageBytes;
+  FastSmemTail& tail = *reinterpret_cast<FastSmemTail*>(smem + kStages * kStageBytes);
+  volatile int* abort_flag = &tail.abort_flag;
+
+  const CanonProblem& p = fp.p;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&tail.full[s], 1);
+      mbar_init(&tail.empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tail.acc_full[b], 1);
+      mbar_init(&tail.acc_empty[b], kEpilogueThreads);
+    }
+    tail.abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(&tail.tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  sched_init<kBM, kBN>(p, tail.sched);  // ends with __syncthreads()
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  tcgen05_fence_after_sync();
+
+  const uint32_t tmem_base = tail.tmem_base;
+  const int total = tail.sched.total;
+  const int a_batched = (p.mode == MODE_UNIFORM);
+  const int b_batched = (p.mode != MODE_KRAGGED);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (one thread)
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+        const TileInfo ti = decode_tile<kBM, kBN>(p, tail.sched, t);
+        const int nkb = (ti.klen + kBK - 1) / kBK;
+        const int az = a_batched ? ti.g : 0;
+        const int bz = b_batched ? ti.g : 0;
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!mbar_wait(&tail.empty[s], ph ^ 1, abort_flag)) {
+            atomicCAS(p.status, 0, ST_PRODUCER_TIMEOUT);
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(&tail.full[s], kStageBytes);
+          const int k = ti.k0 + kb * kBK;
+          uint8_t* sa = smem_a + s * kAStageBytes;
+          uint8_t* sb = smem_b + s * kBStageBytes;
+          if (!fp.a_mn) {
+            tma_load_3d(sa, &tmap_a, &tail.full[s], k, ti.m0, az);
+          } else {
+#pragma unroll
+            for (int c = 0; c < kBM / 64; ++c)
+              tma_load_3d(sa + c * kChunkBytes, &tmap_a, &tail.full[s], ti.m0 + c * 64, k, az);
+          }
+          if (!fp.b_mn) {
+            tma_load_3d(sb, &tmap_b, &tail.full[s], k, ti.n0, bz);
+          } else {
+#pragma unroll
+            for (int c = 0; c < kBN / 64; ++c)
+              tma_load_3d(sb + c * kChunkBytes, &tmap_b, &tail.full[s], ti.n0 + c * 64, k, bz);
+          }
+          if (++s == kStages) { s = 0; ph ^= 1; }
+        }
+      }
+      if (!ok) {
+        // Give copies already in flight a bounded time to land before the CTA exits.
+        for (int i = 0; i < kStages; ++i) {
+          const long long t0 = clock64();
+          while (clock64() - t0 < 2000000LL) {
+            if (mbar_try_wait(&tail.full[i], 0) || mbar_try_wait(&tail.full[i], 1)) break;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (lane 0 issues)
+    // Descriptor geometry. K-major tile: rows of 128 B, 8-row swizzle atoms 1024 B apart; a
+    // 16-element k-step advances 32 B inside the swizzled row. MN-major tile: 64-wide MN
+    // chunks of [64 k-rows][128 B]; chunks are kChunkBytes apart (leading offset), 8-k-row atoms
+    // 1024 B apart (stride offset); a 16-row k-step advances 2048 B.
+    const uint32_t a_lbo = fp.a_mn ? kChunkBytes : 16;
+    const uint32_t b_lbo = fp.b_mn ? kChunkBytes : 16;
+    const uint32_t a_kstep = fp.a_mn ? (kUmmaK * 128) : (kUmmaK * 2);
+    const uint32_t b_kstep = fp.b_mn ? (kUmmaK * 128) : (kUmmaK * 2);
+    int s = 0;
+    uint32_t ph = 0;
+    int it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total && ok; t += gridDim.x, ++it) {
+      const TileInfo ti = decode_tile<kBM, kBN>(p, tail.sched, t);
+      const int nkb = (ti.klen + kBK - 1) / kBK;
+      const int buf = it & 1;
+      const uint32_t aph = (it >> 1) & 1;
+      if (!mbar_wait(&tail.acc_empty[buf], aph ^ 1, abort_flag)) {
+        if (lane == 0) atomicCAS(p.status, 0, ST_MMA_TIMEOUT);
+        ok = false;
+        break;
+      }
+      tcgen05_fence_after_sync();
+      const uint32_t d_tmem = tmem_base + buf * kBN;
+      for (int kb = 0; kb < nkb; ++kb) {
+        if (!mbar_wait(&tail.full[s], ph, abort_flag)) {
+          if (lane == 0) atomicCAS(p.status, 0, ST_MMA_TIMEOUT + 0x10);
+          ok = false;
+          break;
+        }
+        tcgen05_fence_after_sync();
+        uint8_t* sa = smem_a + s * kAStageBytes;
+        uint8_t* sb = smem_b + s * kBStageBytes;
+        if constexpr (KRAGGED) {
+          // The last k-block of a group over-reads k-rows of the next group. Both operands are
+          // MN-major here, so k-rows are whole 128-byte lines: rows [r, 64) of every chunk form
+          // one contiguous range, zeroed before the MMA so they contribute exactly 0.
+          const int r = ti.klen - kb * kBK;
+          if (r < kBK) {
+            const int n16 = (kBK - r) * 8;  // 16-byte words per chunk
+            const uint4 z = make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int c = 0; c < kBM / 64; ++c) {
+              uint4* q = reinterpret_cast<uint4*>(sa + c * kChunkBytes + r * 128);
+              for (int i = lane; i < n16; i += 32) q[i] = z;
+            }
+#pragma unroll
+            for (int c = 0; c < kBN / 64; ++c) {
+              uint4* q = reinterpret_cast<uint4*>(sb + c * kChunkBytes + r * 128);
+              for (int i = lane; i < n16; i += 32) q[i] = z;
+            }
+            fence_proxy_async_smem();
+          }
+          __syncwarp();
+        }
+        if (lane == 0) {
+          const uint64_t a_desc = make_smem_desc_sw128(smem_u32(sa), a_lbo, 1024);
+          const uint64_t b_desc = make_smem_desc_sw128(smem_u32(sb), b_lbo, 1024);
+#pragma unroll
+          for (int k = 0; k < kBK / kUmmaK; ++k) {
+            umma_f16_ss(d_tmem, a_desc + ((k * a_kstep) >> 4), b_desc + ((k * b_kstep) >> 4), fp.idesc,
+                        (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&tail.empty[s]);  // frees the stage once these MMAs have read it
+        }
+        __syncwarp();
+        if (++s == kStages) { s = 0; ph ^= 1; }
+      }
+      if (ok && lane == 0) umma_commit(&tail.acc_full[buf]);
+      __syncwarp();
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;              // TMEM lane quarter this warp may read
+    const int row_in_tile = q * 32 + lane;
+    TOut* c_base = reinterpret_cast<TOut*>(p.c);
+    int it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total && ok; t += gridDim.x, ++it) {
+      const TileInfo ti = decode_tile<kBM, kBN>(p, tail.sched, t);
+      const int buf = it & 1;
+      const uint32_t aph = (it >> 1) & 1;
+      if (!mbar_wait(&tail.acc_full[buf], aph, abort_flag)) {
+        if (lane == 0) atomicCAS(p.status, 0, ST_EPILOGUE_TIMEOUT);
+        ok = false;
+        break;
+      }
+      tcgen05_fence_after_sync();
+      const bool row_ok = row_in_tile < ti.rows;
+      const bool zero_tile = (ti.klen == 0);  // empty KRAGGED group: the block is all zeros
+      TOut* c_row = c_base + (long long)ti.g * p.c_sg + (long long)(ti.m0 + row_in_tile) * p.c_sm +
+                    (long long)ti.n0 * p.c_sn;
+      const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + buf * kBN;
+      const int ncols_tile = min(kBN, p.N - ti.n0);
+#pragma unroll 1
+      for (int c0 = 0; c0 < ncols_tile; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_row + c0, r);
+        tmem_ld_wait();
+        if (zero_tile) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = 0;
+        }
+        if (row_ok) store_row_chunk<TOut>(c_row + (long long)c0 * p.c_sn, p.c_sn, r, min(32, ncols_tile - c0));
+      }
+      tcgen05_fence_before_sync();
+      mbar_arrive(&tail.acc_empty[buf]);
+    }
+  }
+
+  // ------------------------------------------------------------ teardown
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace gmm

@@ -1,0 +1,134 @@
+/*
+ * grouped_mm_b200 — C ABI of the B200 (sm_100a) grouped GEMM library, libgrouped_mm_b200.so.
+ *
+ * This is the drop-in boundary for the forward path of lostmsu/grouped_mm_bf16: the four
+ * functions that the reference's api.py imports from kernels.py and calls with a pre-allocated
+ * output (grouped_mm_bf16/api.py:8-17, call sites api.py:195,201,207,213). Each entry point
+ * below names the reference function it replaces. Conventions, identical to the reference's:
+ * the caller owns every buffer; `out` is written in place; element strides are honoured as
+ * given; the call only enqueues work on the given CUDA stream of the current device and never
+ * synchronises with the host, so `offs` is read on the device only.
+ *
+ * Plain C: pointers and integers only, no C++ or torch types. Every function returns 0 on
+ * success or a negative gmm_status code; gmm_error_string() turns a code into text.
+ */
+#ifndef GROUPED_MM_B200_H_
+#define GROUPED_MM_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GMM_ABI_VERSION 1
+
+/* Element types (reference: _as_tl_dtype, grouped_mm_bf16/kernels.py:175-182). */
+enum gmm_dtype { GMM_BF16 = 0, GMM_F16 = 1, GMM_F32 = 2 };
+
+enum gmm_status {
+  GMM_OK = 0,
+  GMM_ERR_INVALID_ARGUMENT = -1, /* null pointer, bad rank, negative size, mismatched shapes */
+  GMM_ERR_UNSUPPORTED_DTYPE = -2,
+  GMM_ERR_TOO_MANY_GROUPS = -3,  /* more than 1023 groups (reference: api.py:115-116) */
+  GMM_ERR_WORKSPACE = -4,        /* workspace missing, misaligned or smaller than gmm_workspace_bytes() */
+  GMM_ERR_CUDA = -5,             /* a CUDA runtime/driver call failed; see gmm_last_cuda_error() */
+  GMM_ERR_NOT_SM100 = -6,        /* the current device is not compute capability 10.x */
+  GMM_ERR_DEVICE_WAIT = -7       /* a bounded wait inside a kernel gave up (reported by gmm_check_status) */
+};
+
+/* Which kernel a call is routed to. */
+enum gmm_kernel_kind {
+  GMM_KERNEL_NONE = 0,    /* nothing to launch (empty problem) */
+  GMM_KERNEL_TCGEN05 = 1, /* TMA + tcgen05.mma persistent kernel */
+  GMM_KERNEL_GENERIC = 2  /* any-stride fp32-FMA kernel */
+};
+
+/* Flags for gmm_launch_t.flags. */
+#define GMM_FLAG_FORCE_GENERIC 0x1u /* route to the generic kernel even where the TMA path applies */
+
+/*
+ * A 2-D or 3-D strided tensor in device memory. Sizes and strides are in elements, outermost
+ * dimension first, exactly as torch reports them (the reference passes mat.stride(i) straight
+ * to its kernels: grouped_mm_bf16/kernels.py:535-543).
+ */
+typedef struct gmm_tensor {
+  void* data;
+  int32_t dtype; /* enum gmm_dtype */
+  int32_t ndim;  /* 2 or 3 */
+  int64_t size[3];
+  int64_t stride[3];
+} gmm_tensor_t;
+
+/*
+ * Launch context. `workspace` is device memory owned by the caller, at least
+ * gmm_workspace_bytes() long and 256-byte aligned, zero-filled once when it is allocated; it
+ * may be reused by every later call on the same device. Its first 32-bit word is the device
+ * status word read by gmm_check_status().
+ */
+typedef struct gmm_launch {
+  void* stream; /* cudaStream_t; NULL = the legacy default stream */
+  void* workspace;
+  size_t workspace_bytes;
+  uint32_t flags;
+} gmm_launch_t;
+
+int gmm_abi_version(void);
+const char* gmm_error_string(int status);
+/* Text of the last CUDA error seen by the calling thread inside this library ("" if none). */
+const char* gmm_last_cuda_error(void);
+size_t gmm_workspace_bytes(void);
+
+/*
+ * out[g] = a[g] @ b[g]; a [G,M,K], b [G,K,N], out [G,M,N].
+ * Replaces grouped_mm_3d3d(mat_a, mat_b, out), grouped_mm_bf16/kernels.py:524-550.
+ */
+int grouped_mm_3d3d(const gmm_tensor_t* a, const gmm_tensor_t* b, const gmm_tensor_t* out,
+                    const gmm_launch_t* launch);
+
+/*
+ * out[g] = a[:, ks:ke] @ b[ks:ke, :] with [ks,ke) = [offs[g-1], offs[g]); a [M,K_total],
+ * b [K_total,N], out [G,M,N]; an empty range stores zeros.
+ * Replaces grouped_mm_2d2d(mat_a, mat_b, offs, out), grouped_mm_bf16/kernels.py:553-580.
+ */
+int grouped_mm_2d2d(const gmm_tensor_t* a, const gmm_tensor_t* b, const int32_t* offs, int32_t n_groups,
+                    const gmm_tensor_t* out, const gmm_launch_t* launch);
+
+/*
+ * out[r,:] = a[r,:] @ b[g(r)] where group g owns rows [offs[g-1], offs[g]); a [M_total,K],
+ * b [G,K,N], out [M_total,N]. Rows at or past offs[G-1] are left untouched.
+ * Replaces grouped_mm_2d3d(mat_a, mat_b, offs, out), grouped_mm_bf16/kernels.py:583-686.
+ */
+int grouped_mm_2d3d(const gmm_tensor_t* a, const gmm_tensor_t* b, const int32_t* offs, int32_t n_groups,
+                    const gmm_tensor_t* out, const gmm_launch_t* launch);
+
+/*
+ * out[:,c] = a[g(c)] @ b[:,c] where group g owns columns [offs[g-1], offs[g]); a [G,M,K],
+ * b [K,N_total], out [M,N_total]. Columns at or past offs[G-1] are left untouched.
+ * Replaces grouped_mm_3d2d(mat_a, mat_b, offs, out), grouped_mm_bf16/kernels.py:689-717.
+ */
+int grouped_mm_3d2d(const gmm_tensor_t* a, const gmm_tensor_t* b, const int32_t* offs, int32_t n_groups,
+                    const gmm_tensor_t* out, const gmm_launch_t* launch);
+
+/*
+ * Which kernel the corresponding grouped_mm_* call would use for these arguments (enum
+ * gmm_kernel_kind, or a negative gmm_status). `form`: 0 = 3d3d, 1 = 2d3d, 2 = 3d2d, 3 = 2d2d.
+ * Launches nothing. No counterpart in the reference, whose kernels take any strides.
+ */
+int gmm_select_kernel(int32_t form, const gmm_tensor_t* a, const gmm_tensor_t* b, const gmm_tensor_t* out,
+                      uint32_t flags);
+
+/*
+ * Waits for `stream`, reads the status word of `workspace` and clears it. Returns GMM_OK, or
+ * GMM_ERR_DEVICE_WAIT if a kernel gave up on a bounded wait (its outputs are then invalid);
+ * *raw, when not NULL, receives the device code. Diagnostic only: the forward calls never
+ * need it. No counterpart in the reference, whose device code reports no errors.
+ */
+int gmm_check_status(void* workspace, void* stream, int32_t* raw);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* GROUPED_MM_B200_H_ */

@@ -1,0 +1,431 @@
+"""GPU parity: the CUDA path against the CPU oracle, the golden fixtures and size-independent
+properties. Tolerance (from the operator's specification): |out - ref| <= 8e-3 |ref| + 1e-2 sqrt(K) sigma_a sigma_b,
+with ref the fp32 per-group matmul of the same bf16 inputs; fp32 inputs are held to 3e-4.
+"""
+
+import ctypes
+import os
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from grouped_mm_bf16_b200 import _lib, _op, grouped_mm
+from grouped_mm_bf16_b200.workloads import group_sizes, make_workload
+from oracle.grouped_mm_oracle import atol_for, group_bounds, grouped_mm_oracle, max_violation
+
+DEV = torch.device("cuda")
+FORMS = {"3d3d": _lib.FORM_3D3D, "2d3d": _lib.FORM_2D3D, "3d2d": _lib.FORM_3D2D, "2d2d": _lib.FORM_2D2D}
+
+
+@pytest.fixture(autouse=True)
+def _status_word_stays_clear(built_library):
+    yield
+    assert _op.check_status(DEV) == 0, "a bounded wait inside a kernel gave up"
+
+
+class force_generic:
+    def __enter__(self):
+        self.prev = os.environ.get("GROUPED_MM_B200_FORCE_GENERIC")
+        os.environ["GROUPED_MM_B200_FORCE_GENERIC"] = "1"
+
+    def __exit__(self, *exc):
+        if self.prev is None:
+            os.environ.pop("GROUPED_MM_B200_FORCE_GENERIC", None)
+        else:
+            os.environ["GROUPED_MM_B200_FORCE_GENERIC"] = self.prev
+
+
+def _offs(sizes):
+    return torch.tensor(sizes, dtype=torch.int64).cumsum(0).to(torch.int32).to(DEV)
+
+
+def _form(a, b):
+    return {(2, 3): "2d3d", (3, 3): "3d3d", (3, 2): "3d2d", (2, 2): "2d2d"}[(a.dim(), b.dim())]
+
+
+def _assert_parity(a, b, offs, sigma_a, sigma_b, out_dtype=None, expect_kernel=None):
+    """Runs the operator and checks it against the oracle with the specification's tolerance."""
+    out = grouped_mm(a, b, offs=offs, out_dtype=out_dtype)
+    ref, defined = grouped_mm_oracle(a, b, offs)
+    form = _form(a, b)
+    if expect_kernel is not None:
+        assert _op.selected_kernel(FORMS[form], a, b, out) == expect_kernel
+    if form == "2d2d":
+        # K is the group's own length; an empty group must be exactly zero.
+        for g, (s, e) in enumerate(group_bounds(offs.cpu(), a.size(1))):
+            v = max_violation(out[g], ref[g], defined[g], atol_for(e - s, sigma_a, sigma_b))
+            assert v <= 1.0, f"group {g} (k range {s}:{e}) violates tolerance by {v:.3g}x"
+    else:
+        v = max_violation(out, ref, defined, atol_for(a.size(-1), sigma_a, sigma_b))
+        assert v <= 1.0, f"violates tolerance by {v:.3g}x"
+    return out
+
+
+# ----------------------------------------------------------------------------- golden fixtures
+
+
+def test_golden_fixtures_on_gpu(golden_cases):
+    for c in golden_cases:
+        a, b = c["a"].to(DEV), c["b"].to(DEV)
+        assert a.stride() == c["a"].stride() and b.stride() == c["b"].stride()
+        offs = None if c["offs"] is None else c["offs"].to(DEV)
+        out = grouped_mm(a, b, offs=offs)
+        _, defined = grouped_mm_oracle(c["a"], c["b"], c["offs"])
+        got, want = out.float().cpu()[defined], c["out"].float()[defined]
+        if a.dtype == torch.float32:
+            torch.testing.assert_close(got, want, atol=3e-4, rtol=3e-4)
+        else:
+            torch.testing.assert_close(got, want, atol=2e-2, rtol=2e-2)
+
+
+# ----------------------------------------------------------------------------- the five configurations
+
+
+def test_readme_config_through_the_c_abi(built_library):
+    """Config 1, called through the raw C entry point with pointers, sizes and strides."""
+    wl = make_workload("readme", DEV, seed=0)
+    lib = _lib.load()
+    out = torch.full((32, 48), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ws = torch.zeros(64, dtype=torch.int32, device=DEV)
+    a, b, c = _op._desc(wl.mat_a), _op._desc(wl.mat_b), _op._desc(out)
+    launch = _lib.GmmLaunch()
+    launch.stream = torch.cuda.current_stream().cuda_stream
+    launch.workspace, launch.workspace_bytes, launch.flags = ws.data_ptr(), ws.numel() * 4, 0
+    rc = lib.grouped_mm_2d3d(ctypes.byref(a), ctypes.byref(b), ctypes.c_void_p(wl.offs.data_ptr()), 6,
+                             ctypes.byref(c), ctypes.byref(launch))
+    assert rc == 0, _lib.error_message(lib, rc)
+    raw = ctypes.c_int32(-1)
+    assert lib.gmm_check_status(ctypes.c_void_p(ws.data_ptr()), ctypes.c_void_p(launch.stream), ctypes.byref(raw)) == 0
+    assert raw.value == 0
+    ref, defined = grouped_mm_oracle(wl.mat_a, wl.mat_b, wl.offs)
+    assert bool(defined.all())
+    assert max_violation(out, ref, defined, atol_for(64, 1.0, 1.0)) <= 1.0
+
+
+@pytest.mark.parametrize("generic", [False, True])
+@pytest.mark.parametrize("name,scale,dims_scale", [
+    ("readme", 1.0, 1.0),
+    ("batched", 1.0, 1 / 8),
+    ("mixtral", 1 / 16, 1 / 8),
+    ("deepseek_up", 1 / 16, 1 / 8),
+    ("deepseek_down", 1 / 16, 1 / 8),
+    ("wgrad", 1 / 16, 1 / 8),
+])
+def test_scaled_configs_match_oracle(name, scale, dims_scale, generic):
+    wl = make_workload(name, DEV, seed=0, scale=scale, dims_scale=dims_scale)
+    if generic:
+        with force_generic():
+            _assert_parity(wl.mat_a, wl.mat_b, wl.offs, wl.sigma_a, wl.sigma_b, wl.out_dtype, _lib.GMM_KERNEL_GENERIC)
+    else:
+        _assert_parity(wl.mat_a, wl.mat_b, wl.offs, wl.sigma_a, wl.sigma_b, wl.out_dtype, _lib.GMM_KERNEL_TCGEN05)
+
+
+def test_deepseek_variant_with_forced_empty_groups():
+    sizes = group_sizes("deepseek_up", 0, 1 / 16)
+    sizes = [0 if i % 3 == 1 else s for i, s in enumerate(sizes)]
+    wl = make_workload("deepseek_up", DEV, seed=0, dims_scale=1 / 8, sizes=sizes)
+    _assert_parity(wl.mat_a, wl.mat_b, wl.offs, wl.sigma_a, wl.sigma_b, None, _lib.GMM_KERNEL_TCGEN05)
+
+
+# ----------------------------------------------------------------------------- tile-boundary cases
+
+M_PATTERNS = [
+    [128, 128, 128],            # every group a whole tile
+    [127, 1, 128],              # single-row group ending on a tile boundary
+    [129, 0, 255, 1],           # one row past a tile, empty group, one row short of two tiles
+    [40, 30, 10, 7],            # several groups inside one tile
+    [0, 0, 300, 0, 0],          # leading and trailing empties
+    [1, 0] * 12,                # alternating single rows and empties
+    [5, 0, 7, 0, 3, 9],
+    [32, 16, 0, 0, 0],
+    [700],                      # one group, several tiles with a tail
+]
+
+
+@pytest.mark.parametrize("sizes", M_PATTERNS)
+@pytest.mark.parametrize("k,n,b_col_major", [(64, 48, False), (200, 264, False), (72, 520, True), (8, 8, True)])
+def test_2d3d_tile_boundaries_tcgen05(sizes, k, n, b_col_major):
+    g = torch.Generator(device=DEV).manual_seed(len(sizes) * 1000 + k + n)
+    a = torch.randn((sum(sizes), k), device=DEV, generator=g).bfloat16()
+    if b_col_major:
+        b = torch.randn((len(sizes), n, k), device=DEV, generator=g).bfloat16().transpose(-2, -1)
+    else:
+        b = torch.randn((len(sizes), k, n), device=DEV, generator=g).bfloat16()
+    _assert_parity(a, b, _offs(sizes), 1.0, 1.0, None, _lib.GMM_KERNEL_TCGEN05)
+
+
+@pytest.mark.parametrize("sizes", M_PATTERNS[:6])
+def test_2d3d_odd_shapes_generic(sizes):
+    g = torch.Generator(device=DEV).manual_seed(7)
+    k, n = 33, 29
+    a = torch.randn((sum(sizes), k), device=DEV, generator=g).bfloat16()
+    b = torch.randn((len(sizes), k, n), device=DEV, generator=g).bfloat16()
+    _assert_parity(a, b, _offs(sizes), 1.0, 1.0, None, _lib.GMM_KERNEL_GENERIC)
+
+
+K_PATTERNS = [[64, 64], [8, 0, 16, 24, 8], [7, 0, 1, 13, 11], [63, 65, 1, 127], [0, 0, 200], [300, 0, 0]]
+
+
+@pytest.mark.parametrize("sizes", K_PATTERNS)
+@pytest.mark.parametrize("m,n", [(16, 24), (136, 264), (128, 256)])
+@pytest.mark.parametrize("out_dtype", [None, torch.float32])
+def test_2d2d_k_ragged_tcgen05(sizes, m, n, out_dtype):
+    g = torch.Generator(device=DEV).manual_seed(sum(sizes) + m)
+    kt = sum(sizes)
+    a = torch.randn((kt, m), device=DEV, generator=g).bfloat16().t()  # column-major [M, K_total]
+    b = torch.randn((kt, n), device=DEV, generator=g).bfloat16()
+    _assert_parity(a, b, _offs(sizes), 1.0, 1.0, out_dtype, _lib.GMM_KERNEL_TCGEN05)
+
+
+@pytest.mark.parametrize("sizes", K_PATTERNS)
+def test_2d2d_row_major_a_generic(sizes):
+    g = torch.Generator(device=DEV).manual_seed(11)
+    kt = sum(sizes)
+    a = torch.randn((16, kt), device=DEV, generator=g).bfloat16()
+    b = torch.randn((kt, 24), device=DEV, generator=g).bfloat16()
+    _assert_parity(a, b, _offs(sizes), 1.0, 1.0, None, _lib.GMM_KERNEL_GENERIC)
+
+
+@pytest.mark.parametrize("sizes", [[7, 0, 1, 13, 11], [128, 130, 0, 60], [1, 0] * 10])
+@pytest.mark.parametrize("b_col_major,kernel", [(True, _lib.GMM_KERNEL_TCGEN05), (False, _lib.GMM_KERNEL_GENERIC)])
+def test_3d2d_n_ragged(sizes, b_col_major, kernel):
+    g = torch.Generator(device=DEV).manual_seed(13)
+    m, k, nt = 40, 48, sum(sizes)
+    a = torch.randn((len(sizes), m, k), device=DEV, generator=g).bfloat16()
+    b = torch.randn((nt, k), device=DEV, generator=g).bfloat16().t() if b_col_major else \
+        torch.randn((k, nt), device=DEV, generator=g).bfloat16()
+    # the output's leading stride is padded to 16 bytes; nt here is not always a multiple of 8
+    _assert_parity(a, b, _offs(sizes), 1.0, 1.0, None, kernel)
+
+
+@pytest.mark.parametrize("a_col_major", [False, True])
+@pytest.mark.parametrize("b_col_major", [False, True])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_3d3d_all_layouts(a_col_major, b_col_major, dtype):
+    g = torch.Generator(device=DEV).manual_seed(17)
+    G, m, k, n = 3, 136, 200, 264
+    a = torch.randn((G, k, m), device=DEV, generator=g).to(dtype).transpose(-2, -1) if a_col_major else \
+        torch.randn((G, m, k), device=DEV, generator=g).to(dtype)
+    b = torch.randn((G, n, k), device=DEV, generator=g).to(dtype).transpose(-2, -1) if b_col_major else \
+        torch.randn((G, k, n), device=DEV, generator=g).to(dtype)
+    _assert_parity(a, b, None, 1.0, 1.0, None, _lib.GMM_KERNEL_TCGEN05)
+
+
+def test_fp32_inputs_are_true_fp32():
+    g = torch.Generator(device=DEV).manual_seed(19)
+    sizes = [0, 7, 1, 13, 0, 11]
+    a = torch.randn((32, 29), device=DEV, generator=g)
+    b = torch.randn((6, 29, 31), device=DEV, generator=g)
+    out = grouped_mm(a, b, offs=_offs(sizes))
+    ref, _ = grouped_mm_oracle(a, b, _offs(sizes))
+    torch.testing.assert_close(out.cpu(), ref, atol=3e-4, rtol=3e-4)
+
+
+@pytest.mark.parametrize("form", ["2d3d", "3d2d", "2d2d"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_1023_groups(form, dtype):
+    """Alternating one-element and empty groups with a trailing empty group
+    (the reference's large-group-count cases, tests/test_grouped_mm.py:661-747)."""
+    sizes = [1 if i % 2 == 0 else 0 for i in range(1023)]
+    sizes[-1] = 0
+    offs, total = _offs(sizes), sum(sizes)
+    g = torch.Generator(device=DEV).manual_seed(23)
+    if form == "2d3d":
+        a = torch.randn((total, 8), device=DEV, generator=g).to(dtype)
+        b = torch.randn((1023, 8, 8), device=DEV, generator=g).to(dtype)
+    elif form == "3d2d":
+        a = torch.randn((1023, 4, 8), device=DEV, generator=g).to(dtype)
+        b = torch.randn((total, 8), device=DEV, generator=g).to(dtype).t()
+    else:
+        a = torch.randn((total, 8), device=DEV, generator=g).to(dtype).t()
+        b = torch.randn((total, 8), device=DEV, generator=g).to(dtype)
+    if dtype == torch.float32:
+        out = grouped_mm(a, b, offs=offs)
+        ref, defined = grouped_mm_oracle(a, b, offs)
+        torch.testing.assert_close(out.cpu()[defined], ref[defined], atol=3e-4, rtol=3e-4)
+    else:
+        _assert_parity(a, b, offs, 1.0, 1.0)
+
+
+# ----------------------------------------------------------------------------- what must not be written
+
+
+@pytest.mark.parametrize("generic", [False, True])
+def test_guard_bands_stay_untouched(generic):
+    """Padding columns, rows past offs[-1] and memory around the output keep their sentinel."""
+    sizes = [100, 0, 29, 130]  # offs[-1] = 259 < 300 rows
+    k, n, n_pad, rows = 64, 40, 48, 300
+    g = torch.Generator(device=DEV).manual_seed(29)
+    a = torch.randn((rows, k), device=DEV, generator=g).bfloat16()
+    b = torch.randn((4, k, n), device=DEV, generator=g).bfloat16()
+    sentinel = 12345.0
+    buf = torch.full((rows + 16, n_pad), sentinel, dtype=torch.bfloat16, device=DEV)
+    out = buf[8:8 + rows, :n]
+    offs = _offs(sizes)
+    if generic:
+        with force_generic():
+            _op.grouped_mm_2d3d(a, b, offs, out)
+    else:
+        assert _op.selected_kernel(_lib.FORM_2D3D, a, b, out) == _lib.GMM_KERNEL_TCGEN05
+        _op.grouped_mm_2d3d(a, b, offs, out)
+    ref, defined = grouped_mm_oracle(a, b, offs)
+    assert max_violation(out, ref, defined, atol_for(k, 1.0, 1.0)) <= 1.0
+    assert bool((buf[:8] == sentinel).all()) and bool((buf[8 + rows:] == sentinel).all())
+    assert bool((buf[:, n:] == sentinel).all()), "padding columns were written"
+    assert bool((out[259:] == sentinel).all()), "rows past offs[-1] were written"
+
+
+def test_offsets_beyond_the_extent_are_clamped():
+    g = torch.Generator(device=DEV).manual_seed(31)
+    a = torch.randn((40, 64), device=DEV, generator=g).bfloat16()
+    b = torch.randn((3, 64, 48), device=DEV, generator=g).bfloat16()
+    offs = torch.tensor([10, 25, 1000], dtype=torch.int32, device=DEV)
+    _assert_parity(a, b, offs, 1.0, 1.0)
+
+
+def test_results_are_bitwise_reproducible():
+    wl = make_workload("mixtral", DEV, seed=1, scale=1 / 16, dims_scale=1 / 8)
+    first = grouped_mm(wl.mat_a, wl.mat_b, offs=wl.offs)
+    for _ in range(3):
+        assert torch.equal(first, grouped_mm(wl.mat_a, wl.mat_b, offs=wl.offs))
+    wl = make_workload("wgrad", DEV, seed=1, scale=1 / 16, dims_scale=1 / 8)
+    first = grouped_mm(wl.mat_a, wl.mat_b, offs=wl.offs, out_dtype=torch.float32)
+    assert torch.equal(first, grouped_mm(wl.mat_a, wl.mat_b, offs=wl.offs, out_dtype=torch.float32))
+
+
+def test_zero_k_and_empty_outputs():
+    a = torch.zeros((5, 0), dtype=torch.bfloat16, device=DEV)
+    b = torch.zeros((2, 0, 8), dtype=torch.bfloat16, device=DEV)
+    out = grouped_mm(a, b, offs=_offs([2, 3]))
+    assert out.shape == (5, 8) and float(out.abs().sum()) == 0.0
+    a = torch.zeros((0, 16), dtype=torch.bfloat16, device=DEV)
+    b = torch.zeros((2, 16, 8), dtype=torch.bfloat16, device=DEV)
+    assert grouped_mm(a, b, offs=_offs([0, 0])).shape == (0, 8)
+
+
+def test_output_strides_are_padded_like_the_reference():
+    a = torch.randn((32, 33), device=DEV).bfloat16()
+    b = torch.randn((6, 33, 29), device=DEV).bfloat16()
+    out = grouped_mm(a, b, offs=_offs([0, 7, 1, 13, 0, 11]))
+    assert out.shape == (32, 29) and out.stride() == (32, 1)
+    a3, b3 = torch.randn((3, 17, 19), device=DEV), torch.randn((3, 19, 23), device=DEV)
+    assert grouped_mm(a3, b3).stride() == (17 * 24, 24, 1)
+
+
+# ----------------------------------------------------------------------------- argument rules that need CUDA tensors
+
+
+def test_offs_and_bias_rules():
+    a = torch.zeros((8, 16), dtype=torch.bfloat16, device=DEV)
+    b = torch.zeros((2, 16, 8), dtype=torch.bfloat16, device=DEV)
+    offs = _offs([4, 4])
+    with pytest.raises(RuntimeError, match="Have to provide offsets"):
+        grouped_mm(a, b)
+    with pytest.raises(RuntimeError, match="Have to provide offsets"):
+        grouped_mm(torch.zeros((2, 8, 16), dtype=torch.bfloat16, device=DEV), b, offs=offs)
+    with pytest.raises(RuntimeError, match="offs must be a CUDA/HIP tensor"):
+        grouped_mm(a, b, offs=offs.cpu())
+    with pytest.raises(RuntimeError, match="offs has to be 1D"):
+        grouped_mm(a, b, offs=offs.view(1, 2))
+    with pytest.raises(RuntimeError, match="Offsets have to be int32"):
+        grouped_mm(a, b, offs=offs.long())
+    with pytest.raises(RuntimeError, match="Can't process more than 1024 groups"):
+        grouped_mm(a, torch.zeros((1024, 16, 8), dtype=torch.bfloat16, device=DEV),
+                   offs=torch.zeros(1024, dtype=torch.int32, device=DEV))
+    with pytest.raises(RuntimeError, match="Bias not supported yet"):
+        grouped_mm(a, b, offs=offs, bias=torch.zeros(8, device=DEV))
+    with pytest.raises(RuntimeError, match="output dtype must match"):
+        grouped_mm(a, b, offs=offs, out_dtype=torch.float16)
+    with pytest.raises(RuntimeError, match="matrix batch sizes have to match"):
+        grouped_mm(a, b, offs=_offs([4, 2, 2]))
+    with pytest.raises(RuntimeError, match="Invalid strides/sizes"):
+        grouped_mm(torch.zeros((8, 32), dtype=torch.bfloat16, device=DEV)[:, ::2], b, offs=offs)
+
+
+def test_strict_alignment_mode(monkeypatch):
+    a = torch.zeros((8, 33), dtype=torch.bfloat16, device=DEV)
+    b = torch.zeros((2, 33, 8), dtype=torch.bfloat16, device=DEV)
+    grouped_mm(a, b, offs=_offs([4, 4]))  # accepted by default, as in the reference
+    monkeypatch.setenv("GROUPED_MM_B200_STRICT_ALIGN", "1")
+    with pytest.raises(RuntimeError, match="multiple of 16 bytes"):
+        grouped_mm(a, b, offs=_offs([4, 4]))
+
+
+# ----------------------------------------------------------------------------- full-size configurations
+
+
+def _sampled_row_check(wl, out, rows_per_group=3, max_groups=24):
+    """Checks sampled rows of a full-size 2D x 3D result against the oracle on the CPU."""
+    bounds = group_bounds(wl.offs.cpu(), wl.mat_a.size(0))
+    live = [g for g, (s, e) in enumerate(bounds) if e > s]
+    step = max(1, len(live) // max_groups)
+    atol = atol_for(wl.k, wl.sigma_a, wl.sigma_b)
+    for g in live[::step]:
+        s, e = bounds[g]
+        rows = sorted({s, e - 1, (s + e) // 2})[:rows_per_group]
+        idx = torch.tensor(rows, device=DEV)
+        ref = wl.mat_a[idx].float().cpu() @ wl.mat_b[g].float().cpu()
+        v = max_violation(out[idx], ref, torch.ones_like(ref, dtype=torch.bool), atol)
+        assert v <= 1.0, f"group {g} rows {rows}: tolerance exceeded {v:.3g}x"
+
+
+def test_mixtral_full_size_properties():
+    wl = make_workload("mixtral", DEV, seed=0)
+    assert wl.mat_a.shape == (32768, 4096) and wl.mat_b.shape == (8, 4096, 14336)
+    out = grouped_mm(wl.mat_a, wl.mat_b, offs=wl.offs)
+    assert _op.selected_kernel(_lib.FORM_2D3D, wl.mat_a, wl.mat_b, out) == _lib.GMM_KERNEL_TCGEN05
+    _sampled_row_check(wl, out)
+    # homogeneity: scaling A by a power of two scales the result exactly (bf16 exponent shift)
+    assert torch.equal(grouped_mm(wl.mat_a * 2, wl.mat_b, offs=wl.offs), out * 2)
+    # group independence: permuting the weights of two groups only changes those groups' rows
+    b2 = wl.mat_b.clone()
+    b2[[2, 3]] = wl.mat_b[[3, 2]]
+    out2 = grouped_mm(wl.mat_a, b2, offs=wl.offs)
+    bounds = group_bounds(wl.offs.cpu(), 32768)
+    assert torch.equal(out2[: bounds[2][0]], out[: bounds[2][0]]) and torch.equal(out2[bounds[3][1]:], out[bounds[3][1]:])
+    assert torch.isfinite(out.float()).all()
+
+
+@pytest.mark.parametrize("name", ["deepseek_up", "deepseek_down"])
+def test_deepseek_full_size_sampled_rows(name):
+    wl = make_workload(name, DEV, seed=0)
+    assert wl.mat_b.stride(-2) == 1  # column-major weights
+    out = grouped_mm(wl.mat_a, wl.mat_b, offs=wl.offs)
+    assert _op.selected_kernel(_lib.FORM_2D3D, wl.mat_a, wl.mat_b, out) == _lib.GMM_KERNEL_TCGEN05
+    _sampled_row_check(wl, out, rows_per_group=2, max_groups=32)
+
+
+def test_batched_full_size_against_oracle_sample():
+    wl = make_workload("batched", DEV, seed=0)
+    out = grouped_mm(wl.mat_a, wl.mat_b)
+    atol = atol_for(wl.k, wl.sigma_a, wl.sigma_b)
+    for g in (0, 7, 15):
+        rows = torch.tensor([0, 511, 1023], device=DEV)
+        ref = wl.mat_a[g][rows].float().cpu() @ wl.mat_b[g].float().cpu()
+        assert max_violation(out[g][rows], ref, torch.ones_like(ref, dtype=torch.bool), atol) <= 1.0
+
+
+def test_wgrad_full_size_groups_and_checksum():
+    wl = make_workload("wgrad", DEV, seed=0)
+    assert wl.mat_a.shape == (4096, 65536) and wl.mat_a.stride() == (1, 4096)
+    out = grouped_mm(wl.mat_a, wl.mat_b, offs=wl.offs, out_dtype=torch.float32)
+    assert out.dtype == torch.float32 and out.shape == (64, 4096, 1536)
+    assert _op.selected_kernel(_lib.FORM_2D2D, wl.mat_a, wl.mat_b, out) == _lib.GMM_KERNEL_TCGEN05
+    bounds = group_bounds(wl.offs.cpu(), 65536)
+    empties = [g for g, (s, e) in enumerate(bounds) if e == s]
+    assert empties, "the seeded draw has empty groups"
+    for g in empties:
+        assert float(out[g].abs().max()) == 0.0
+    for g in (0, 17, 40, 63):
+        s, e = bounds[g]
+        if e > s:
+            rows = torch.tensor([0, 2047, 4095], device=DEV)
+            ref = wl.mat_a[rows, s:e].float().cpu() @ wl.mat_b[s:e].float().cpu()
+            assert max_violation(out[g][rows], ref, torch.ones_like(ref, dtype=torch.bool), atol_for(e - s, 1, 1)) <= 1.0
+    # the sum over groups of a K-partitioned product is the plain product A @ B
+    rows = torch.tensor([5, 1000, 4000], device=DEV)
+    total = out[:, rows, :].sum(0).cpu()
+    ref = wl.mat_a[rows].float().cpu() @ wl.mat_b.float().cpu()
+    torch.testing.assert_close(total, ref, atol=atol_for(65536, 1, 1), rtol=8e-3)

@@ -1,0 +1,136 @@
+"""The reference's acceptance cases, restated: forward and backward of all four shape forms
+against stock torch ops, with the reference's group-size patterns and tolerances
+(tests/test_grouped_mm.py in lostmsu/grouped_mm_bf16: bf16 forward 2e-2, fp32 forward 3e-4,
+bf16 backward 4e-2..6e-2, fp32 backward 2e-4..8e-4). The tile knobs the reference's tests set
+through GROUPED_MM_2D3D_* environment variables are accepted and ignored here.
+"""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from grouped_mm_bf16 import grouped_mm
+
+DEV = torch.device("cuda")
+
+
+def _offs(sizes):
+    return torch.tensor(sizes, dtype=torch.int32, device=DEV).cumsum(0).to(torch.int32)
+
+
+def _gid(offs, total):
+    return torch.searchsorted(offs, torch.arange(total, device=DEV, dtype=torch.int32), right=True).long()
+
+
+def _ref_2d3d(a, b, offs):
+    return torch.bmm(a.unsqueeze(1), b.index_select(0, _gid(offs, a.size(0)))).squeeze(1)
+
+
+def _ref_2d2d(a, b, offs):
+    k = torch.arange(a.size(1), device=DEV, dtype=torch.int32)
+    start = torch.cat([torch.zeros(1, device=DEV, dtype=torch.int32), offs[:-1]])
+    mask = (k[None] >= start[:, None]) & (k[None] < offs[:, None])
+    return torch.matmul(a.unsqueeze(0) * mask.to(a.dtype).unsqueeze(1), b)
+
+
+def _ref_3d2d(a, b, offs):
+    a_g = a.index_select(0, _gid(offs, b.size(1)))
+    return torch.bmm(a_g, b.t().unsqueeze(-1)).squeeze(-1).t()
+
+
+def _tol(dtype, fwd):
+    if dtype == torch.float32:
+        return dict(atol=3e-4, rtol=3e-4) if fwd else dict(atol=8e-4, rtol=8e-4)
+    return dict(atol=2e-2, rtol=2e-2) if fwd else dict(atol=6e-2, rtol=6e-2)
+
+
+def _fwd_bwd(a0, b0, offs, ref_fn, dtype, bwd_tol=None):
+    a1, b1 = a0.clone().requires_grad_(True), b0.clone().requires_grad_(True)
+    out = grouped_mm(a1, b1, offs=offs)
+    a2, b2 = a0.clone().requires_grad_(True), b0.clone().requires_grad_(True)
+    ref = ref_fn(a2, b2) if offs is None else ref_fn(a2, b2, offs)
+    torch.testing.assert_close(out, ref, **_tol(dtype, True))
+    w = torch.randn_like(ref)
+    da, db = torch.autograd.grad((out * w).sum(), [a1, b1])
+    da_ref, db_ref = torch.autograd.grad((ref * w).sum(), [a2, b2])
+    tol = bwd_tol or _tol(dtype, False)
+    torch.testing.assert_close(da, da_ref, **tol)
+    torch.testing.assert_close(db, db_ref, **tol)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("shape", [(4, 32, 64, 48), (3, 17, 19, 23)])
+def test_3d3d_forward_backward(dtype, shape):
+    g, m, k, n = shape
+    _fwd_bwd(torch.randn((g, m, k), device=DEV, dtype=dtype), torch.randn((g, k, n), device=DEV, dtype=dtype),
+             None, torch.bmm, dtype)
+
+
+SIZE_PATTERNS = [
+    [0, 7, 1, 13, 0, 11], [32, 32, 32], [10, 10, 10, 2], [31, 1, 31], [40, 30, 10, 7], [32, 16, 0, 0, 0],
+    [1, 0] * 6, [5, 0, 7, 0, 3, 9], [32, 1, 30], [11, 90, 7], [0, 3, 0, 0, 5, 0, 1, 0, 9],
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("sizes", SIZE_PATTERNS)
+@pytest.mark.parametrize("k,n", [(32, 40), (33, 29), (64, 48)])
+def test_2d3d_forward_backward(dtype, sizes, k, n, monkeypatch):
+    for key, val in (("GROUPED_MM_2D3D_IMPL", "prologue"), ("GROUPED_MM_2D3D_BLOCK_M", "32"),
+                     ("GROUPED_MM_2D3D_BLOCK_N", "64"), ("GROUPED_MM_2D3D_BLOCK_K", "32"),
+                     ("GROUPED_MM_2D3D_NUM_WARPS", "4")):
+        monkeypatch.setenv(key, val)
+    torch.manual_seed(0)
+    a = torch.randn((sum(sizes), k), device=DEV, dtype=dtype)
+    b = torch.randn((len(sizes), k, n), device=DEV, dtype=dtype)
+    bwd = dict(atol=0.6, rtol=0.1) if dtype == torch.bfloat16 and max(sizes) >= 64 else None
+    _fwd_bwd(a, b, _offs(sizes), _ref_2d3d, dtype, bwd)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("sizes", [[7, 0, 1, 13, 11], [8, 0, 16, 24, 8]])
+def test_2d2d_forward_backward(dtype, sizes):
+    a = torch.randn((16, sum(sizes)), device=DEV, dtype=dtype)
+    b = torch.randn((sum(sizes), 24), device=DEV, dtype=dtype)
+    _fwd_bwd(a, b, _offs(sizes), _ref_2d2d, dtype)
+    # the weight-gradient layout (column-major A) takes the tensor-core path when aligned
+    a_t = torch.randn((sum(sizes), 16), device=DEV, dtype=dtype).t()
+    _fwd_bwd(a_t, b, _offs(sizes), _ref_2d2d, dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("sizes", [[7, 0, 1, 13, 11], [8, 0, 16, 24, 8]])
+def test_3d2d_forward_backward(dtype, sizes):
+    a = torch.randn((len(sizes), 32, 48), device=DEV, dtype=dtype)
+    b = torch.randn((48, sum(sizes)), device=DEV, dtype=dtype)
+    _fwd_bwd(a, b, _offs(sizes), _ref_3d2d, dtype)
+    b_t = torch.randn((sum(sizes), 48), device=DEV, dtype=dtype).t()
+    _fwd_bwd(a, b_t, _offs(sizes), _ref_3d2d, dtype)
+
+
+@pytest.mark.parametrize("form", ["2d3d", "3d2d", "2d2d"])
+def test_1023_groups_fp32_forward_backward(form):
+    sizes = torch.zeros(1023, dtype=torch.int32, device=DEV)
+    sizes[::2] = 1
+    sizes[-1] = 0
+    offs = sizes.cumsum(0).to(torch.int32)
+    total = int(offs[-1].item())
+    if form == "2d3d":
+        a, b, ref_fn = torch.randn((total, 8), device=DEV), torch.randn((1023, 8, 8), device=DEV), _ref_2d3d
+    elif form == "3d2d":
+        a, b, ref_fn = torch.randn((1023, 4, 8), device=DEV), torch.randn((8, total), device=DEV), _ref_3d2d
+    else:
+        a, b, ref_fn = torch.randn((4, total), device=DEV), torch.randn((total, 8), device=DEV), _ref_2d2d
+    _fwd_bwd(a, b, offs, ref_fn, torch.float32)
+
+
+def test_readme_example():
+    a = torch.randn((4, 32, 64), device=DEV, dtype=torch.bfloat16)
+    b = torch.randn((4, 64, 48), device=DEV, dtype=torch.bfloat16)
+    torch.testing.assert_close(grouped_mm(a, b), torch.bmm(a, b), atol=2e-2, rtol=2e-2)
+    sizes = torch.tensor([0, 7, 1, 13, 0, 11], device=DEV, dtype=torch.int32)
+    offs = sizes.cumsum(0).to(torch.int32)
+    a = torch.randn((int(offs[-1].item()), 64), device=DEV, dtype=torch.bfloat16)
+    b = torch.randn((sizes.numel(), 64, 48), device=DEV, dtype=torch.bfloat16)
+    torch.testing.assert_close(grouped_mm(a, b, offs=offs), _ref_2d3d(a, b, offs), atol=2e-2, rtol=2e-2)
