@@ -142,6 +142,7 @@ gmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
     tail.abort_flag = 0;
     fence_barrier_init();
+    fence_proxy_async_smem();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
   }

@@ -54,9 +54,9 @@ def _fwd_bwd(a0, b0, offs, ref_fn, dtype, bwd_tol=None):
     w = torch.randn_like(ref)
     da, db = torch.autograd.grad((out * w).sum(), [a1, b1])
     da_ref, db_ref = torch.autograd.grad((ref * w).sum(), [a2, b2])
-    tol = bwd_tol or _tol(dtype, False)
+    tol = _tol(dtype, False)
     torch.testing.assert_close(da, da_ref, **tol)
-    torch.testing.assert_close(db, db_ref, **tol)
+    torch.testing.assert_close(db, db_ref, **(bwd_tol or tol))
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
@@ -84,7 +84,9 @@ def test_2d3d_forward_backward(dtype, sizes, k, n, monkeypatch):
     torch.manual_seed(0)
     a = torch.randn((sum(sizes), k), device=DEV, dtype=dtype)
     b = torch.randn((len(sizes), k, n), device=DEV, dtype=dtype)
-    bwd = dict(atol=0.6, rtol=0.1) if dtype == torch.bfloat16 and max(sizes) >= 64 else None
+    # torch's own bf16 weight gradient (index_select backward) accumulates in bf16; the reference's
+    # test allows atol 0.6 / rtol 0.1 for it (tests/test_grouped_mm.py:512).
+    bwd = dict(atol=0.6, rtol=0.1) if dtype == torch.bfloat16 else None
     _fwd_bwd(a, b, _offs(sizes), _ref_2d3d, dtype, bwd)
 
 
