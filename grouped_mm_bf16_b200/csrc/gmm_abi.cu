@@ -5,6 +5,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <cstdlib>
 #include <mutex>
 #include <string>
 
@@ -12,6 +13,7 @@
 #include "gmm_common.cuh"
 #include "gmm_generic_kernel.cuh"
 #include "gmm_sm100_kernel.cuh"
+#include "gmm_sm100_pair_kernel.cuh"
 
 namespace {
 
@@ -59,8 +61,8 @@ EncodeTiledFn get_encode() {
 }
 
 template <typename K>
-int set_smem_attr(K kernel) {
-  GMM_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFastSmemBytes));
+int set_smem_attr(K kernel, size_t bytes = kFastSmemBytes) {
+  GMM_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
   return GMM_OK;
 }
 
@@ -78,6 +80,9 @@ int init_device(int dev) {
     if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_kernel<true, __nv_bfloat16>);
     if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_kernel<true, __half>);
     if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_kernel<true, float>);
+    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_pair_kernel<__nv_bfloat16>, kPairSmemBytes);
+    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_pair_kernel<__half>, kPairSmemBytes);
+    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_pair_kernel<float>, kPairSmemBytes);
     d.status = rc;
   });
   return d.status;
@@ -189,14 +194,20 @@ struct FastPlan {
   bool ok = false;
   int a_mn = 0;
   int b_mn = 0;
+  bool pair = false;  // CTA-pair kernel (256-row tiles) instead of the single-CTA kernel (128-row tiles)
 };
+
+int env_int(const char* name, int fallback) {
+  const char* v = std::getenv(name);
+  return (v && *v) ? std::atoi(v) : fallback;
+}
 
 bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; }
 
 // The TMA path needs 16-bit inputs, 16-byte aligned bases and leading/group strides, and the
 // ragged dimension must not be the contiguous one (a group may start at any index of it, while a
 // TMA box must start on a 16-byte boundary of the contiguous dimension).
-FastPlan plan_fast(const CanonProblem& p) {
+FastPlan plan_fast(const CanonProblem& p, uint32_t flags) {
   FastPlan f;
   if (p.in_dtype == DT_F32 || p.K < 1) return f;
   if (!aligned16(p.a) || !aligned16(p.b)) return f;
@@ -211,6 +222,17 @@ FastPlan plan_fast(const CanonProblem& p) {
   if (p.mode == MODE_MRAGGED && f.a_mn) return f;
   if (p.mode == MODE_KRAGGED && !(f.a_mn && f.b_mn)) return f;
   f.ok = true;
+  // 256-row pair tiles pay off when groups are tall (little tail waste) and N spans both halves.
+  // The group sizes live on the device, so the host decides on the mean rows per group.
+  if (p.mode != MODE_KRAGGED && p.N > kPairBNHalf) {
+    const long long mean_rows = (p.mode == MODE_MRAGGED) ? (long long)p.M / (p.G > 0 ? p.G : 1) : p.M;
+    f.pair = mean_rows >= 768;
+    if (flags & GMM_FLAG_FORCE_PAIR) f.pair = true;
+    if (flags & GMM_FLAG_NO_PAIR) f.pair = false;
+    const int env = env_int("GROUPED_MM_B200_PAIR", -1);  // tuning knob: 0 / 1 overrides the heuristic
+    if (env == 0) f.pair = false;
+    if (env == 1) f.pair = true;
+  }
   return f;
 }
 
@@ -240,7 +262,7 @@ int encode_map(CUtensorMap* map, const void* base, int in_dtype, long long inner
   return GMM_OK;
 }
 
-uint32_t make_idesc(int in_dtype, int a_mn, int b_mn) {
+uint32_t make_idesc(int in_dtype, int a_mn, int b_mn, int mma_m) {
   const uint32_t fmt = (in_dtype == DT_BF16) ? 1u : 0u;  // 0 = f16, 1 = bf16
   uint32_t d = 0;
   d |= 1u << 4;                        // accumulator format: f32
@@ -249,7 +271,7 @@ uint32_t make_idesc(int in_dtype, int a_mn, int b_mn) {
   d |= (uint32_t)(a_mn ? 1 : 0) << 15; // A major: 0 = K, 1 = MN
   d |= (uint32_t)(b_mn ? 1 : 0) << 16; // B major
   d |= (uint32_t)(kBN >> 3) << 17;     // N / 8
-  d |= (uint32_t)(kBM >> 4) << 24;     // M / 16
+  d |= (uint32_t)(mma_m >> 4) << 24;   // M / 16 (128 for one CTA, 256 for a CTA pair)
   return d;
 }
 
@@ -304,23 +326,47 @@ int launch_fast_kr(const CUtensorMap& ta, const CUtensorMap& tb, const FastParam
   return GMM_OK;
 }
 
-int launch_fast(const CanonProblem& p, const FastPlan& plan, const DeviceInfo& d, cudaStream_t st) {
-  const long long ub = tile_upper_bound(p, kBM, kBN);
+template <typename TOut>
+int launch_pair_t(const CUtensorMap& ta, const CUtensorMap& tb, const FastParams& fp, int grid, cudaStream_t st) {
+  gmm_sm100_pair_kernel<TOut><<<grid, kFastThreads, kPairSmemBytes, st>>>(ta, tb, fp);
+  GMM_CUDA_TRY(cudaGetLastError());
+  return GMM_OK;
+}
+
+// n-tiles per B panel: as many as keep one panel (panel x BN columns x K rows) within a budget
+// that stays resident in L2 while every m-tile of the group is swept over it.
+int choose_panel(const CanonProblem& p) {
+  const int env = env_int("GROUPED_MM_B200_PANEL", 0);  // tuning knob
+  if (env > 0) return env;
+  const long long tile_bytes = (long long)kBN * p.K * 2;
+  long long panel = (32ll << 20) / (tile_bytes > 0 ? tile_bytes : 1);
+  if (panel < 2) panel = 2;
+  if (panel > 64) panel = 64;
+  return (int)panel;
+}
+
+int launch_fast(const CanonProblem& p_in, const FastPlan& plan, const DeviceInfo& d, cudaStream_t st) {
+  CanonProblem p = p_in;
+  const int bm = plan.pair ? kPairBM : kBM;
+  p.panel = choose_panel(p);
+  const long long ub = tile_upper_bound(p, bm, kBN);
   if (ub <= 0) return GMM_OK;
   if (ub > 0x7fffffffLL) return GMM_ERR_INVALID_ARGUMENT;
-  const int grid = (int)(ub < d.sm_count ? ub : d.sm_count);
+  const int units = plan.pair ? d.sm_count / 2 : d.sm_count;
+  const int grid = (int)(ub < units ? ub : units) * (plan.pair ? 2 : 1);
 
   const bool a_batched = (p.mode == MODE_UNIFORM);
   const bool b_batched = (p.mode != MODE_KRAGGED);
   CUtensorMap ta, tb;
   int rc;
   if (!plan.a_mn)
-    rc = encode_map(&ta, p.a, p.in_dtype, p.K, p.M, a_batched ? p.G : 1, p.a_sm, p.a_sg, kBM);
+    rc = encode_map(&ta, p.a, p.in_dtype, p.K, p.M, a_batched ? p.G : 1, p.a_sm, p.a_sg, 128);
   else
     rc = encode_map(&ta, p.a, p.in_dtype, p.M, p.K, a_batched ? p.G : 1, p.a_sk, p.a_sg, kBK);
   if (rc != GMM_OK) return rc;
   if (!plan.b_mn)
-    rc = encode_map(&tb, p.b, p.in_dtype, p.K, p.N, b_batched ? p.G : 1, p.b_sn, p.b_sg, kBN);
+    rc = encode_map(&tb, p.b, p.in_dtype, p.K, p.N, b_batched ? p.G : 1, p.b_sn, p.b_sg,
+                    plan.pair ? kPairBNHalf : kBN);
   else
     rc = encode_map(&tb, p.b, p.in_dtype, p.N, p.K, b_batched ? p.G : 1, p.b_sk, p.b_sg, kBK);
   if (rc != GMM_OK) return rc;
@@ -329,7 +375,14 @@ int launch_fast(const CanonProblem& p, const FastPlan& plan, const DeviceInfo& d
   fp.p = p;
   fp.a_mn = plan.a_mn;
   fp.b_mn = plan.b_mn;
-  fp.idesc = make_idesc(p.in_dtype, plan.a_mn, plan.b_mn);
+  fp.idesc = make_idesc(p.in_dtype, plan.a_mn, plan.b_mn, plan.pair ? 256 : 128);
+  if (plan.pair) {
+    switch (p.out_dtype) {
+      case DT_BF16: return launch_pair_t<__nv_bfloat16>(ta, tb, fp, grid, st);
+      case DT_F16: return launch_pair_t<__half>(ta, tb, fp, grid, st);
+      default: return launch_pair_t<float>(ta, tb, fp, grid, st);
+    }
+  }
   return p.mode == MODE_KRAGGED ? launch_fast_kr<true>(ta, tb, fp, grid, st)
                                 : launch_fast_kr<false>(ta, tb, fp, grid, st);
 }
@@ -357,7 +410,7 @@ int run(int form, const gmm_tensor_t* a, const gmm_tensor_t* b, const int32_t* o
   const DeviceInfo& d = g_dev[dev];
   cudaStream_t st = reinterpret_cast<cudaStream_t>(launch->stream);
 
-  const FastPlan plan = (launch->flags & GMM_FLAG_FORCE_GENERIC) ? FastPlan() : plan_fast(p);
+  const FastPlan plan = (launch->flags & GMM_FLAG_FORCE_GENERIC) ? FastPlan() : plan_fast(p, launch->flags);
   return plan.ok ? launch_fast(p, plan, d, st) : launch_generic(p, d, st);
 }
 
@@ -419,7 +472,7 @@ int gmm_select_kernel(int32_t form, const gmm_tensor_t* a, const gmm_tensor_t* b
   if (rc != GMM_OK) return rc;
   if (nothing) return GMM_KERNEL_NONE;
   if (flags & GMM_FLAG_FORCE_GENERIC) return GMM_KERNEL_GENERIC;
-  return plan_fast(p).ok ? GMM_KERNEL_TCGEN05 : GMM_KERNEL_GENERIC;
+  return plan_fast(p, flags).ok ? GMM_KERNEL_TCGEN05 : GMM_KERNEL_GENERIC;
 }
 
 int gmm_check_status(void* workspace, void* stream, int32_t* raw) {

@@ -37,6 +37,7 @@ struct CanonProblem {
   long long c_sg, c_sm, c_sn;
   int in_dtype;
   int out_dtype;
+  int panel;    // n-tiles per resident B panel (0 = default); see decode_tile
   int* status;  // device word; stays 0 unless a bounded wait gave up
 };
 
@@ -57,9 +58,10 @@ struct SchedSmem {
   int m_tiles;                 // m-tiles per group (UNIFORM, KRAGGED)
   int n_tiles;
   int total;                   // total tiles
+  int panel;                   // n-tiles per B panel
 };
 
-constexpr int kBand = 8;  // m-tiles that share one sweep over the n-tiles (L2 reuse of A and B panels)
+constexpr int kDefaultPanel = 16;
 
 // Builds the schedule in shared memory. Called by every thread of the block; ends with a barrier.
 template <int BM, int BN>
@@ -67,6 +69,7 @@ __device__ __forceinline__ void sched_init(const CanonProblem& p, SchedSmem& s) 
   const int tid = threadIdx.x;
   const int nthr = blockDim.x;
   const int n_tiles = (p.N + BN - 1) / BN;
+  if (tid == 0) s.panel = p.panel > 0 ? p.panel : kDefaultPanel;
   if (p.mode == MODE_UNIFORM) {
     if (tid == 0) {
       s.m_tiles = (p.M + BM - 1) / BM;
@@ -130,42 +133,53 @@ __device__ __forceinline__ void sched_init(const CanonProblem& p, SchedSmem& s) 
   __syncthreads();
 }
 
-// Maps a linear tile index to its work item. Tiles are ordered in bands of kBand m-tiles; inside
-// a band the n-tile is the slow index, so the CTAs running at the same time share A and B panels.
+// Maps a linear tile index to its work item. Tiles are ordered group by group; inside a group the
+// n-tiles are cut into panels of `panel` tiles, and for each panel all m-tiles of the group are
+// swept with the n-tile as the fast index. The CTAs running at the same time therefore work on one
+// B panel (panel x BN columns, which stays in L2 for the whole sweep) and on a few consecutive
+// m-tiles of A, each shared by `panel` CTAs: B is read from HBM once, A once per panel.
 template <int BM, int BN>
 __device__ __forceinline__ TileInfo decode_tile(const CanonProblem& p, const SchedSmem& s, int t) {
-  const int band_tiles = kBand * s.n_tiles;
-  const int band = t / band_tiles;
-  const int w = t - band * band_tiles;
-  const int band_m0 = band * kBand;
-  const int bsz = min(kBand, s.mt_total - band_m0);
-  const int nt = w / bsz;
-  const int mtg = band_m0 + (w - nt * bsz);
-
   TileInfo ti;
-  ti.n0 = nt * BN;
+  int g, idx, mt_g, start = 0;
   if (p.mode == MODE_MRAGGED) {
+    const int key = t / s.n_tiles;  // group g holds tiles [prefix[g] * n_tiles, prefix[g+1] * n_tiles)
     int lo = 0, hi = p.G - 1;
     while (lo < hi) {
       const int mid = (lo + hi + 1) >> 1;
-      if (s.prefix[mid] <= mtg) lo = mid; else hi = mid - 1;
+      if (s.prefix[mid] <= key) lo = mid; else hi = mid - 1;
     }
-    const int start = lo ? s.ends[lo - 1] : 0;
-    ti.g = lo;
-    ti.m0 = start + (mtg - s.prefix[lo]) * BM;
-    ti.rows = min(BM, s.ends[lo] - ti.m0);
+    g = lo;
+    idx = t - s.prefix[g] * s.n_tiles;
+    mt_g = s.prefix[g + 1] - s.prefix[g];
+    start = g ? s.ends[g - 1] : 0;
+  } else {
+    const int per_group = s.m_tiles * s.n_tiles;
+    g = t / per_group;
+    idx = t - g * per_group;
+    mt_g = s.m_tiles;
+  }
+  const int panel_tiles = mt_g * s.panel;
+  const int ns = idx / panel_tiles;
+  const int rem = idx - ns * panel_tiles;
+  const int width = min(s.panel, s.n_tiles - ns * s.panel);
+  const int mt = rem / width;
+  const int nt = ns * s.panel + (rem - mt * width);
+
+  ti.g = g;
+  ti.n0 = nt * BN;
+  if (p.mode == MODE_MRAGGED) {
+    ti.m0 = start + mt * BM;
+    ti.rows = min(BM, s.ends[g] - ti.m0);
     ti.k0 = 0;
     ti.klen = p.K;
   } else {
-    const int g = mtg / s.m_tiles;
-    const int mt = mtg - g * s.m_tiles;
-    ti.g = g;
     ti.m0 = mt * BM;
     ti.rows = min(BM, p.M - ti.m0);
     if (p.mode == MODE_KRAGGED) {
-      const int start = g ? s.ends[g - 1] : 0;
-      const int len = s.ends[g] - start;
-      ti.k0 = start;
+      const int ks = g ? s.ends[g - 1] : 0;
+      const int len = s.ends[g] - ks;
+      ti.k0 = ks;
       ti.klen = len > 0 ? len : 0;
     } else {
       ti.k0 = 0;

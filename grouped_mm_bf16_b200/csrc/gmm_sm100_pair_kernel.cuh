@@ -1,0 +1,228 @@
+// CTA-pair variant of the persistent grouped GEMM for sm_100a (UNIFORM and MRAGGED modes).
+//
+// Two CTAs on the two SMs of one TPC (a cluster of 2) share every 256 x 256 output tile:
+// CTA r loads rows [128 r, 128 r + 128) of the A tile and columns [128 r, 128 r + 128) of the B
+// tile into its own shared memory, the leader (r = 0) issues tcgen05.mma.cta_group::2
+// (256 x 256 x 16), which reads both CTAs' shared memory and accumulates rows 128 r.. into CTA r's
+// tensor memory, and each CTA's epilogue warps store their own 128 rows. Per SM this moves 32 KiB
+// per 64-deep k-block from L2 instead of the 48 KiB of the single-CTA kernel, and leaves room for a
+// 6-stage ring; both are what the single-CTA kernel is short of on large problems.
+//
+// Every TMA load has exactly one destination CTA. Cross-CTA signalling uses mbarriers only:
+//   full[s]      lives in the leader; both CTAs' loads credit their bytes to it
+//   empty[s]     one per CTA; the leader's tcgen05.commit arrives on both
+//   acc_full[b]  one per CTA; same
+//   acc_empty[b] lives in the leader; the 2 x 128 epilogue threads arrive on it
+#pragma once
+
+#include "gmm_sm100_kernel.cuh"
+
+namespace gmm {
+
+constexpr int kPairBM = 256;       // rows of a pair tile (128 per CTA)
+constexpr int kPairBNHalf = 128;   // B columns held by one CTA
+constexpr int kPairStages = 6;
+constexpr int kPairAStageBytes = 128 * kBK * 2;            // 16 KiB
+constexpr int kPairBStageBytes = kPairBNHalf * kBK * 2;    // 16 KiB
+constexpr int kPairStageBytes = kPairAStageBytes + kPairBStageBytes;
+
+struct PairSmemTail {
+  uint64_t full[kPairStages];
+  uint64_t empty[kPairStages];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+  SchedSmem sched;
+};
+
+constexpr size_t kPairSmemBytes = 1024 + size_t(kPairStages) * kPairStageBytes + sizeof(PairSmemTail);
+
+enum PairStatus : int {
+  ST_PAIR_PRODUCER_TIMEOUT = 0x201,
+  ST_PAIR_MMA_TIMEOUT = 0x202,
+  ST_PAIR_EPILOGUE_TIMEOUT = 0x203,
+};
+
+template <typename TOut>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFastThreads, 1)
+gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                      const FastParams fp) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_a = smem;
+  uint8_t* smem_b = smem + kPairStages * kPairAStageBytes;
+  PairSmemTail& tail = *reinterpret_cast<PairSmemTail*>(smem + kPairStages * kPairStageBytes);
+  volatile int* abort_flag = &tail.abort_flag;
+
+  const CanonProblem& p = fp.p;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 = leader
+  const int pair = blockIdx.x >> 1;
+  const int n_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPairStages; ++s) {
+      mbar_init(&tail.full[s], 1);
+      mbar_init(&tail.empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tail.acc_full[b], 1);
+      mbar_init(&tail.acc_empty[b], 2 * kEpilogueThreads);
+    }
+    tail.abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(&tail.tmem_base, kTmemCols);
+    tmem_relinquish_pair();
+  }
+  sched_init<kPairBM, kBN>(p, tail.sched);
+  tcgen05_fence_before_sync();
+  cluster_sync_all();  // barriers of both CTAs are initialised before anyone signals across
+  tcgen05_fence_after_sync();
+
+  const uint32_t tmem_base = tail.tmem_base;
+  const int total = tail.sched.total;
+  const int a_batched = (p.mode == MODE_UNIFORM);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (one thread per CTA)
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int t = pair; t < total && ok; t += n_pairs) {
+        const TileInfo ti = decode_tile<kPairBM, kBN>(p, tail.sched, t);
+        const int nkb = (ti.klen + kBK - 1) / kBK;
+        const int az = a_batched ? ti.g : 0;
+        const int row0 = ti.m0 + int(rank) * 128;
+        const int col0 = ti.n0 + int(rank) * kPairBNHalf;
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!mbar_wait(&tail.empty[s], ph ^ 1, abort_flag)) {
+            atomicCAS(p.status, 0, ST_PAIR_PRODUCER_TIMEOUT);
+            ok = false;
+            break;
+          }
+          if (rank == 0) mbar_arrive_expect_tx(&tail.full[s], 2 * kPairStageBytes);
+          const uint32_t full_leader = map_to_cta(smem_u32(&tail.full[s]), 0);
+          const int k = kb * kBK;
+          uint8_t* sa = smem_a + s * kPairAStageBytes;
+          uint8_t* sb = smem_b + s * kPairBStageBytes;
+          if (!fp.a_mn) {
+            tma_load_3d_pair(sa, &tmap_a, full_leader, k, row0, az);
+          } else {
+#pragma unroll
+            for (int c = 0; c < 2; ++c) tma_load_3d_pair(sa + c * kChunkBytes, &tmap_a, full_leader, row0 + c * 64, k, az);
+          }
+          if (!fp.b_mn) {
+            tma_load_3d_pair(sb, &tmap_b, full_leader, k, col0, ti.g);
+          } else {
+#pragma unroll
+            for (int c = 0; c < 2; ++c) tma_load_3d_pair(sb + c * kChunkBytes, &tmap_b, full_leader, col0 + c * 64, k, ti.g);
+          }
+          if (++s == kPairStages) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader CTA, lane 0)
+    if (rank == 0) {
+      const uint32_t a_lbo = fp.a_mn ? kChunkBytes : 16;
+      const uint32_t b_lbo = fp.b_mn ? kChunkBytes : 16;
+      const uint32_t a_kstep = fp.a_mn ? (kUmmaK * 128) : (kUmmaK * 2);
+      const uint32_t b_kstep = fp.b_mn ? (kUmmaK * 128) : (kUmmaK * 2);
+      int s = 0;
+      uint32_t ph = 0;
+      int it = 0;
+      bool ok = true;
+      for (int t = pair; t < total && ok; t += n_pairs, ++it) {
+        const TileInfo ti = decode_tile<kPairBM, kBN>(p, tail.sched, t);
+        const int nkb = (ti.klen + kBK - 1) / kBK;
+        const int buf = it & 1;
+        const uint32_t aph = (it >> 1) & 1;
+        if (!mbar_wait(&tail.acc_empty[buf], aph ^ 1, abort_flag)) {
+          if (lane == 0) atomicCAS(p.status, 0, ST_PAIR_MMA_TIMEOUT);
+          ok = false;
+          break;
+        }
+        tcgen05_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + buf * kBN;
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!mbar_wait(&tail.full[s], ph, abort_flag)) {
+            if (lane == 0) atomicCAS(p.status, 0, ST_PAIR_MMA_TIMEOUT + 0x10);
+            ok = false;
+            break;
+          }
+          tcgen05_fence_after_sync();
+          if (lane == 0) {
+            const uint64_t a_desc = make_smem_desc_sw128(smem_u32(smem_a + s * kPairAStageBytes), a_lbo, 1024);
+            const uint64_t b_desc = make_smem_desc_sw128(smem_u32(smem_b + s * kPairBStageBytes), b_lbo, 1024);
+#pragma unroll
+            for (int k = 0; k < kBK / kUmmaK; ++k) {
+              umma_f16_ss_pair(d_tmem, a_desc + ((k * a_kstep) >> 4), b_desc + ((k * b_kstep) >> 4), fp.idesc,
+                               (kb | k) != 0 ? 1u : 0u);
+            }
+            umma_commit_pair(&tail.empty[s], 0x3);  // frees the stage in both CTAs
+          }
+          __syncwarp();
+          if (++s == kPairStages) { s = 0; ph ^= 1; }
+        }
+        if (ok && lane == 0) umma_commit_pair(&tail.acc_full[buf], 0x3);
+        __syncwarp();
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5 of both CTAs)
+    const int q = warp & 3;
+    const int row_in_half = q * 32 + lane;
+    TOut* c_base = reinterpret_cast<TOut*>(p.c);
+    int it = 0;
+    bool ok = true;
+    for (int t = pair; t < total && ok; t += n_pairs, ++it) {
+      const TileInfo ti = decode_tile<kPairBM, kBN>(p, tail.sched, t);
+      const int buf = it & 1;
+      const uint32_t aph = (it >> 1) & 1;
+      if (!mbar_wait(&tail.acc_full[buf], aph, abort_flag)) {
+        if (lane == 0) atomicCAS(p.status, 0, ST_PAIR_EPILOGUE_TIMEOUT);
+        ok = false;
+        break;
+      }
+      tcgen05_fence_after_sync();
+      const int row_in_tile = int(rank) * 128 + row_in_half;
+      const bool row_ok = row_in_tile < ti.rows;
+      TOut* c_row = c_base + (long long)ti.g * p.c_sg + (long long)(ti.m0 + row_in_tile) * p.c_sm +
+                    (long long)ti.n0 * p.c_sn;
+      const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + buf * kBN;
+      const int ncols_tile = min(kBN, p.N - ti.n0);
+      // A CTA whose half of the tile lies wholly past the group's end has nothing to store.
+      const bool half_live = int(rank) * 128 < ti.rows;
+      if (half_live) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < ncols_tile; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(t_row + c0, r);
+          tmem_ld_wait();
+          if (row_ok) store_row_chunk<TOut>(c_row + (long long)c0 * p.c_sn, p.c_sn, r, min(32, ncols_tile - c0));
+        }
+      }
+      tcgen05_fence_before_sync();
+      mbar_arrive_cluster(map_to_cta(smem_u32(&tail.acc_empty[buf]), 0));
+    }
+  }
+
+  // ------------------------------------------------------------ teardown
+  __syncwarp();
+  tcgen05_fence_before_sync();
+  cluster_sync_all();  // neither CTA leaves while its peer may still read its shared memory or signal it
+  if (warp == 1) {
+    tcgen05_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace gmm

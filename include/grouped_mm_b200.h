@@ -47,6 +47,8 @@ enum gmm_kernel_kind {
 
 /* Flags for gmm_launch_t.flags. */
 #define GMM_FLAG_FORCE_GENERIC 0x1u /* route to the generic kernel even where the TMA path applies */
+#define GMM_FLAG_FORCE_PAIR 0x2u    /* tcgen05 path: always use the CTA-pair (cta_group::2) kernel if legal */
+#define GMM_FLAG_NO_PAIR 0x4u       /* tcgen05 path: never use the CTA-pair kernel */
 
 /*
  * A 2-D or 3-D strided tensor in device memory. Sizes and strides are in elements, outermost

@@ -25,6 +25,14 @@ def _status_word_stays_clear(built_library):
     assert _op.check_status(DEV) == 0, "a bounded wait inside a kernel gave up"
 
 
+@pytest.fixture(params=["single_cta", "cta_pair"])
+def tile_kernel(request, monkeypatch):
+    """Runs a test once with the single-CTA (128-row tiles) and once with the CTA-pair
+    (cta_group::2, 256-row tiles) variant of the tcgen05 kernel."""
+    monkeypatch.setenv("GROUPED_MM_B200_PAIR", "1" if request.param == "cta_pair" else "0")
+    return request.param
+
+
 class force_generic:
     def __enter__(self):
         self.prev = os.environ.get("GROUPED_MM_B200_FORCE_GENERIC")
@@ -113,7 +121,7 @@ def test_readme_config_through_the_c_abi(built_library):
     ("deepseek_down", 1 / 16, 1 / 8),
     ("wgrad", 1 / 16, 1 / 8),
 ])
-def test_scaled_configs_match_oracle(name, scale, dims_scale, generic):
+def test_scaled_configs_match_oracle(name, scale, dims_scale, generic, tile_kernel):
     wl = make_workload(name, DEV, seed=0, scale=scale, dims_scale=dims_scale)
     if generic:
         with force_generic():
@@ -141,12 +149,13 @@ M_PATTERNS = [
     [5, 0, 7, 0, 3, 9],
     [32, 16, 0, 0, 0],
     [700],                      # one group, several tiles with a tail
+    [300, 0, 513, 255, 257],    # around the 256-row tiles of the CTA-pair kernel
 ]
 
 
 @pytest.mark.parametrize("sizes", M_PATTERNS)
 @pytest.mark.parametrize("k,n,b_col_major", [(64, 48, False), (200, 264, False), (72, 520, True), (8, 8, True)])
-def test_2d3d_tile_boundaries_tcgen05(sizes, k, n, b_col_major):
+def test_2d3d_tile_boundaries_tcgen05(sizes, k, n, b_col_major, tile_kernel):
     g = torch.Generator(device=DEV).manual_seed(len(sizes) * 1000 + k + n)
     a = torch.randn((sum(sizes), k), device=DEV, generator=g).bfloat16()
     if b_col_major:
@@ -190,7 +199,7 @@ def test_2d2d_row_major_a_generic(sizes):
 
 @pytest.mark.parametrize("sizes", [[7, 0, 1, 13, 11], [128, 130, 0, 60], [1, 0] * 10])
 @pytest.mark.parametrize("b_col_major,kernel", [(True, _lib.GMM_KERNEL_TCGEN05), (False, _lib.GMM_KERNEL_GENERIC)])
-def test_3d2d_n_ragged(sizes, b_col_major, kernel):
+def test_3d2d_n_ragged(sizes, b_col_major, kernel, tile_kernel):
     g = torch.Generator(device=DEV).manual_seed(13)
     m, k, nt = 40, 48, sum(sizes)
     a = torch.randn((len(sizes), m, k), device=DEV, generator=g).bfloat16()
@@ -203,7 +212,7 @@ def test_3d2d_n_ragged(sizes, b_col_major, kernel):
 @pytest.mark.parametrize("a_col_major", [False, True])
 @pytest.mark.parametrize("b_col_major", [False, True])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-def test_3d3d_all_layouts(a_col_major, b_col_major, dtype):
+def test_3d3d_all_layouts(a_col_major, b_col_major, dtype, tile_kernel):
     g = torch.Generator(device=DEV).manual_seed(17)
     G, m, k, n = 3, 136, 200, 264
     a = torch.randn((G, k, m), device=DEV, generator=g).to(dtype).transpose(-2, -1) if a_col_major else \
@@ -253,7 +262,7 @@ def test_1023_groups(form, dtype):
 
 
 @pytest.mark.parametrize("generic", [False, True])
-def test_guard_bands_stay_untouched(generic):
+def test_guard_bands_stay_untouched(generic, tile_kernel):
     """Padding columns, rows past offs[-1] and memory around the output keep their sentinel."""
     sizes = [100, 0, 29, 130]  # offs[-1] = 259 < 300 rows
     k, n, n_pad, rows = 64, 40, 48, 300
@@ -285,7 +294,7 @@ def test_offsets_beyond_the_extent_are_clamped():
     _assert_parity(a, b, offs, 1.0, 1.0)
 
 
-def test_results_are_bitwise_reproducible():
+def test_results_are_bitwise_reproducible(tile_kernel):
     wl = make_workload("mixtral", DEV, seed=1, scale=1 / 16, dims_scale=1 / 8)
     first = grouped_mm(wl.mat_a, wl.mat_b, offs=wl.offs)
     for _ in range(3):
