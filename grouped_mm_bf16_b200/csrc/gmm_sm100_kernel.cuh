@@ -45,7 +45,9 @@ struct FastSmemTail {
   SchedSmem sched;
 };
 
-constexpr size_t kFastSmemBytes = 1024 /*alignment slack*/ + size_t(kStages) * kStageBytes + sizeof(FastSmemTail);
+constexpr int kStageRowBytesFwd = 144;  // see kStageRowBytes below
+constexpr size_t kFastSmemBytes =
+    1024 /*alignment slack*/ + size_t(kStages) * kStageBytes + sizeof(FastSmemTail) + 4 * 32 * kStageRowBytesFwd;
 
 struct FastParams {
   CanonProblem p;
@@ -115,6 +117,87 @@ __device__ __forceinline__ void store_row_chunk(TOut* dst, long long col_stride,
   }
 }
 
+// Per-warp staging area used to turn "one thread = one output row" (the TMEM read layout) into
+// row-contiguous global stores: 32 rows of 128 bytes, padded to 144 so that both the row-wise
+// writes and the transposed reads are free of bank conflicts.
+constexpr int kStageRowBytes = 144;
+constexpr int kWarpStageBytes = 32 * kStageRowBytes;
+constexpr int kEpilogueStageBytes = 4 * kWarpStageBytes;
+
+// Stores this warp's 32 rows of one accumulator tile. `t_row` is the TMEM address of the warp's
+// lane quarter at column 0 of the tile, `c_warp` points at (first row of the warp, first column of
+// the tile), `rows` is how many of the warp's 32 rows are valid (<= 0: none), `ncols` how many of
+// the tile's columns are. Whole-warp call: tcgen05.ld is warp-collective.
+//
+// Fast path (unit column stride, 16-byte aligned rows, full 128-byte chunk): each thread converts
+// 128 bytes of its row and parks them in shared memory; the warp then writes 4 rows x 128 bytes per
+// instruction, i.e. whole cache lines, instead of 32 scattered 16-byte pieces.
+template <typename TOut>
+__device__ __forceinline__ void epilogue_store_warp(uint32_t t_row, TOut* c_warp, long long c_sm, long long c_sn,
+                                                    int rows, int ncols, uint8_t* stage, bool zero_tile, int lane) {
+  constexpr int CW = 128 / (int)sizeof(TOut);  // columns per 128-byte chunk: 32 (fp32) or 64 (16-bit)
+  const bool rows_aligned = (c_sn == 1) && ((reinterpret_cast<uintptr_t>(c_warp) & 15u) == 0) &&
+                            (((c_sm * (long long)sizeof(TOut)) & 15) == 0);
+  const bool row_ok = lane < rows;
+  TOut* c_row = c_warp + (long long)lane * c_sm;
+#pragma unroll 1
+  for (int c0 = 0; c0 < ncols; c0 += CW) {
+    uint32_t r[CW];
+    {
+      uint32_t (&lo)[32] = *reinterpret_cast<uint32_t (*)[32]>(&r[0]);
+      tmem_ld_32x32b_x32(t_row + c0, lo);
+      if constexpr (CW == 64) {
+        uint32_t (&hi)[32] = *reinterpret_cast<uint32_t (*)[32]>(&r[32]);
+        tmem_ld_32x32b_x32(t_row + c0 + 32, hi);
+      }
+      tmem_ld_wait();
+    }
+    if (zero_tile) {
+#pragma unroll
+      for (int i = 0; i < CW; ++i) r[i] = 0;
+    }
+    if (rows_aligned && c0 + CW <= ncols) {
+      uint4* mine = reinterpret_cast<uint4*>(stage + lane * kStageRowBytes);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        uint4 v;
+        if constexpr (sizeof(TOut) == 4) {
+          v = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+        } else {
+          v.x = OutCvt<TOut>::pack2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
+          v.y = OutCvt<TOut>::pack2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+          v.z = OutCvt<TOut>::pack2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+          v.w = OutCvt<TOut>::pack2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+        }
+        mine[j] = v;
+      }
+      __syncwarp();
+      const int seg = lane & 7;   // 16-byte segment of the 128-byte row chunk
+      const int sub = lane >> 3;  // which of the 4 rows of this instruction
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int row = i * 4 + sub;
+        const uint4 v = *reinterpret_cast<const uint4*>(stage + row * kStageRowBytes + seg * 16);
+        if (row < rows) {
+          uint8_t* dst = reinterpret_cast<uint8_t*>(c_warp + (long long)row * c_sm + c0) + seg * 16;
+          *reinterpret_cast<uint4*>(dst) = v;
+        }
+      }
+      __syncwarp();
+    } else if (row_ok) {
+      // Edge chunk, strided or unaligned output: every thread stores its own row.
+      uint32_t (&lo)[32] = *reinterpret_cast<uint32_t (*)[32]>(&r[0]);
+      store_row_chunk<TOut>(c_row + (long long)c0 * c_sn, c_sn, lo, min(32, ncols - c0));
+      if constexpr (CW == 64) {
+        if (c0 + 32 < ncols) {
+          uint32_t (&hi)[32] = *reinterpret_cast<uint32_t (*)[32]>(&r[32]);
+          store_row_chunk<TOut>(c_row + (long long)(c0 + 32) * c_sn, c_sn, hi, min(32, ncols - c0 - 32));
+        }
+      }
+    }
+  }
+}
+
 template <bool KRAGGED, typename TOut>
 __global__ void __launch_bounds__(kFastThreads, 1)
 gmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -125,6 +208,7 @@ gmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   uint8_t* smem_a = smem;
   uint8_t* smem_b = smem + kStages * kAStageBytes;
   FastSmemTail& tail = *reinterpret_cast<FastSmemTail*>(smem + kStages * kStageBytes);
+  uint8_t* epi_stage = smem + kStages * kStageBytes + ((sizeof(FastSmemTail) + 15) & ~size_t(15));
   volatile int* abort_flag = &tail.abort_flag;
 
   const CanonProblem& p = fp.p;
@@ -181,19 +265,19 @@ gmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const int k = ti.k0 + kb * kBK;
           uint8_t* sa = smem_a + s * kAStageBytes;
           uint8_t* sb = smem_b + s * kBStageBytes;
+          auto load_a = [&](void* dst, int x, int y) { tma_load_3d(dst, &tmap_a, &tail.full[s], x, y, az); };
+          auto load_b = [&](void* dst, int x, int y) { tma_load_3d(dst, &tmap_b, &tail.full[s], x, y, bz); };
           if (!fp.a_mn) {
-            tma_load_3d(sa, &tmap_a, &tail.full[s], k, ti.m0, az);
+            load_a(sa, k, ti.m0);
           } else {
 #pragma unroll
-            for (int c = 0; c < kBM / 64; ++c)
-              tma_load_3d(sa + c * kChunkBytes, &tmap_a, &tail.full[s], ti.m0 + c * 64, k, az);
+            for (int c = 0; c < kBM / 64; ++c) load_a(sa + c * kChunkBytes, ti.m0 + c * 64, k);
           }
           if (!fp.b_mn) {
-            tma_load_3d(sb, &tmap_b, &tail.full[s], k, ti.n0, bz);
+            load_b(sb, k, ti.n0);
           } else {
 #pragma unroll
-            for (int c = 0; c < kBN / 64; ++c)
-              tma_load_3d(sb + c * kChunkBytes, &tmap_b, &tail.full[s], ti.n0 + c * 64, k, bz);
+            for (int c = 0; c < kBN / 64; ++c) load_b(sb + c * kChunkBytes, ti.n0 + c * 64, k);
           }
           if (++s == kStages) { s = 0; ph ^= 1; }
         }
@@ -284,7 +368,6 @@ gmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5)
     const int q = warp & 3;              // TMEM lane quarter this warp may read
-    const int row_in_tile = q * 32 + lane;
     TOut* c_base = reinterpret_cast<TOut*>(p.c);
     int it = 0;
     bool ok = true;
@@ -298,23 +381,13 @@ gmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         break;
       }
       tcgen05_fence_after_sync();
-      const bool row_ok = row_in_tile < ti.rows;
       const bool zero_tile = (ti.klen == 0);  // empty KRAGGED group: the block is all zeros
-      TOut* c_row = c_base + (long long)ti.g * p.c_sg + (long long)(ti.m0 + row_in_tile) * p.c_sm +
-                    (long long)ti.n0 * p.c_sn;
+      TOut* c_warp = c_base + (long long)ti.g * p.c_sg + (long long)(ti.m0 + q * 32) * p.c_sm +
+                     (long long)ti.n0 * p.c_sn;
       const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + buf * kBN;
       const int ncols_tile = min(kBN, p.N - ti.n0);
-#pragma unroll 1
-      for (int c0 = 0; c0 < ncols_tile; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(t_row + c0, r);
-        tmem_ld_wait();
-        if (zero_tile) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = 0;
-        }
-        if (row_ok) store_row_chunk<TOut>(c_row + (long long)c0 * p.c_sn, p.c_sn, r, min(32, ncols_tile - c0));
-      }
+      epilogue_store_warp<TOut>(t_row, c_warp, p.c_sm, p.c_sn, ti.rows - q * 32, ncols_tile,
+                                epi_stage + (warp - 2) * kWarpStageBytes, zero_tile, lane);
       tcgen05_fence_before_sync();
       mbar_arrive(&tail.acc_empty[buf]);
     }

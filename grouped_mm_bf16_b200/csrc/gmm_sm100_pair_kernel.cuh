@@ -36,7 +36,8 @@ struct PairSmemTail {
   SchedSmem sched;
 };
 
-constexpr size_t kPairSmemBytes = 1024 + size_t(kPairStages) * kPairStageBytes + sizeof(PairSmemTail);
+constexpr size_t kPairSmemBytes =
+    1024 + size_t(kPairStages) * kPairStageBytes + sizeof(PairSmemTail) + kEpilogueStageBytes;
 
 enum PairStatus : int {
   ST_PAIR_PRODUCER_TIMEOUT = 0x201,
@@ -53,6 +54,7 @@ gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   uint8_t* smem_a = smem;
   uint8_t* smem_b = smem + kPairStages * kPairAStageBytes;
   PairSmemTail& tail = *reinterpret_cast<PairSmemTail*>(smem + kPairStages * kPairStageBytes);
+  uint8_t* epi_stage = smem + kPairStages * kPairStageBytes + ((sizeof(PairSmemTail) + 15) & ~size_t(15));
   volatile int* abort_flag = &tail.abort_flag;
 
   const CanonProblem& p = fp.p;
@@ -113,17 +115,19 @@ gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           const int k = kb * kBK;
           uint8_t* sa = smem_a + s * kPairAStageBytes;
           uint8_t* sb = smem_b + s * kPairBStageBytes;
+          auto load_a = [&](void* dst, int x, int y) { tma_load_3d_pair(dst, &tmap_a, full_leader, x, y, az); };
+          auto load_b = [&](void* dst, int x, int y) { tma_load_3d_pair(dst, &tmap_b, full_leader, x, y, ti.g); };
           if (!fp.a_mn) {
-            tma_load_3d_pair(sa, &tmap_a, full_leader, k, row0, az);
+            load_a(sa, k, row0);
           } else {
 #pragma unroll
-            for (int c = 0; c < 2; ++c) tma_load_3d_pair(sa + c * kChunkBytes, &tmap_a, full_leader, row0 + c * 64, k, az);
+            for (int c = 0; c < 2; ++c) load_a(sa + c * kChunkBytes, row0 + c * 64, k);
           }
           if (!fp.b_mn) {
-            tma_load_3d_pair(sb, &tmap_b, full_leader, k, col0, ti.g);
+            load_b(sb, k, col0);
           } else {
 #pragma unroll
-            for (int c = 0; c < 2; ++c) tma_load_3d_pair(sb + c * kChunkBytes, &tmap_b, full_leader, col0 + c * 64, k, ti.g);
+            for (int c = 0; c < 2; ++c) load_b(sb + c * kChunkBytes, col0 + c * 64, k);
           }
           if (++s == kPairStages) { s = 0; ph ^= 1; }
         }
@@ -179,7 +183,6 @@ gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5 of both CTAs)
     const int q = warp & 3;
-    const int row_in_half = q * 32 + lane;
     TOut* c_base = reinterpret_cast<TOut*>(p.c);
     int it = 0;
     bool ok = true;
@@ -193,23 +196,15 @@ gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         break;
       }
       tcgen05_fence_after_sync();
-      const int row_in_tile = int(rank) * 128 + row_in_half;
-      const bool row_ok = row_in_tile < ti.rows;
-      TOut* c_row = c_base + (long long)ti.g * p.c_sg + (long long)(ti.m0 + row_in_tile) * p.c_sm +
-                    (long long)ti.n0 * p.c_sn;
+      const int row0 = int(rank) * 128 + q * 32;  // first row of this warp inside the pair tile
+      TOut* c_warp = c_base + (long long)ti.g * p.c_sg + (long long)(ti.m0 + row0) * p.c_sm +
+                     (long long)ti.n0 * p.c_sn;
       const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + buf * kBN;
       const int ncols_tile = min(kBN, p.N - ti.n0);
-      // A CTA whose half of the tile lies wholly past the group's end has nothing to store.
-      const bool half_live = int(rank) * 128 < ti.rows;
-      if (half_live) {
-#pragma unroll 1
-        for (int c0 = 0; c0 < ncols_tile; c0 += 32) {
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(t_row + c0, r);
-          tmem_ld_wait();
-          if (row_ok) store_row_chunk<TOut>(c_row + (long long)c0 * p.c_sn, p.c_sn, r, min(32, ncols_tile - c0));
-        }
-      }
+      // A warp whose rows lie wholly past the group's end has nothing to read or store.
+      if (row0 < ti.rows)
+        epilogue_store_warp<TOut>(t_row, c_warp, p.c_sm, p.c_sn, ti.rows - row0, ncols_tile,
+                                  epi_stage + (warp - 2) * kWarpStageBytes, false, lane);
       tcgen05_fence_before_sync();
       mbar_arrive_cluster(map_to_cta(smem_u32(&tail.acc_empty[buf]), 0));
     }
