@@ -34,6 +34,7 @@ constexpr int kChunkBytes = 64 * kBK * 2;            // one 64-wide MN chunk of 
 constexpr int kTmemCols = 512;
 constexpr int kFastThreads = 192;
 constexpr int kEpilogueThreads = 128;
+constexpr unsigned kEpilogueBackoffNs = 128;  // sleep between polls while an epilogue warp waits for a tile
 
 struct FastSmemTail {
   uint64_t full[kStages];
@@ -375,7 +376,7 @@ gmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const TileInfo ti = decode_tile<kBM, kBN>(p, tail.sched, t);
       const int buf = it & 1;
       const uint32_t aph = (it >> 1) & 1;
-      if (!mbar_wait(&tail.acc_full[buf], aph, abort_flag)) {
+      if (!mbar_wait(&tail.acc_full[buf], aph, abort_flag, kEpilogueBackoffNs)) {
         if (lane == 0) atomicCAS(p.status, 0, ST_EPILOGUE_TIMEOUT);
         ok = false;
         break;

@@ -190,7 +190,7 @@ gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       const TileInfo ti = decode_tile<kPairBM, kBN>(p, tail.sched, t);
       const int buf = it & 1;
       const uint32_t aph = (it >> 1) & 1;
-      if (!mbar_wait(&tail.acc_full[buf], aph, abort_flag)) {
+      if (!mbar_wait(&tail.acc_full[buf], aph, abort_flag, kEpilogueBackoffNs)) {
         if (lane == 0) atomicCAS(p.status, 0, ST_PAIR_EPILOGUE_TIMEOUT);
         ok = false;
         break;

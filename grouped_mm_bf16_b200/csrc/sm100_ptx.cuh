@@ -61,7 +61,10 @@ constexpr long long kWaitBudgetCycles = 4000000000LL;
 
 // Waits for the phase with the given parity. `abort_flag` (shared memory, CTA-wide) lets all
 // roles of a CTA leave together once any one of them has given up. Returns false on give-up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+// `backoff_ns` > 0 sleeps between polls: used where the wait is long (an epilogue warp waits
+// for a whole tile's main loop) so that idle warps do not compete for issue slots and power.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          unsigned backoff_ns = 0) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (true) {
@@ -71,6 +74,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
       *abort_flag = 1;
       return false;
     }
+    if (backoff_ns) __nanosleep(backoff_ns);
   }
 }
 
