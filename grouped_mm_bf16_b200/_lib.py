@@ -29,6 +29,7 @@ EXPORTED_SYMBOLS = (
     "grouped_mm_2d2d",
     "grouped_mm_2d3d",
     "grouped_mm_3d2d",
+    "grouped_mm_2d3d_static_scratch",
     "gmm_select_kernel",
     "gmm_check_status",
 )
@@ -86,6 +87,9 @@ def load() -> ctypes.CDLL:
             fn = getattr(lib, name)
             fn.restype = ctypes.c_int
             fn.argtypes = [tp, tp, ctypes.c_void_p, ctypes.c_int32, tp, lp]
+        lib.grouped_mm_2d3d_static_scratch.restype = ctypes.c_int
+        lib.grouped_mm_2d3d_static_scratch.argtypes = [tp, tp, ctypes.c_void_p, ctypes.c_int32, tp, ctypes.c_void_p,
+                                                       ctypes.c_uint32, ctypes.POINTER(ctypes.c_void_p)]
         lib.gmm_select_kernel.restype = ctypes.c_int
         lib.gmm_select_kernel.argtypes = [ctypes.c_int32, tp, tp, tp, ctypes.c_uint32]
         lib.gmm_check_status.restype = ctypes.c_int

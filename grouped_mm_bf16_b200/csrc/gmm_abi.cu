@@ -414,6 +414,39 @@ int run(int form, const gmm_tensor_t* a, const gmm_tensor_t* b, const int32_t* o
   return plan.ok ? launch_fast(p, plan, d, st) : launch_generic(p, d, st);
 }
 
+// ------------------------------------------------------------------ library-owned scratch
+//
+// Scratch for grouped_mm_2d3d_static_scratch(): the same 256-byte block (status word first) that
+// other entry points receive as `workspace`, but owned by the library image itself, so that the
+// caller has nothing to allocate. Every GPU that loads the library holds these 256 bytes until the
+// process exits. In host code the array's name only stands for the symbol; the device address
+// comes from cudaGetSymbolAddress(), once per device, with that device current.
+constexpr size_t kStaticScratchBytes = 256;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+struct StaticScratch {
+  std::once_flag once;
+  int status = GMM_OK;
+  void* ptr = nullptr;
+};
+StaticScratch g_static[kMaxDevices];
+
+// Must run with device `dev` current. The first call on a device does the symbol lookup.
+int static_scratch(int dev, void** ptr) {
+  StaticScratch& ss = g_static[dev];
+  std::call_once(ss.once, [&] {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      ss.status = cuda_fail(e, "cudaGetSymbolAddress(g_static_scratch)");
+      return;
+    }
+    ss.ptr = p;
+  });
+  *ptr = ss.ptr;
+  return ss.status;
+}
+
 }  // namespace
 
 // ====================================================================== C ABI
@@ -458,6 +491,31 @@ int grouped_mm_3d2d(const gmm_tensor_t* a, const gmm_tensor_t* b, const int32_t*
 int grouped_mm_2d2d(const gmm_tensor_t* a, const gmm_tensor_t* b, const int32_t* offs, int32_t n_groups,
                     const gmm_tensor_t* out, const gmm_launch_t* launch) {
   return run(3, a, b, offs, n_groups, out, launch);
+}
+
+int grouped_mm_2d3d_static_scratch(const gmm_tensor_t* a, const gmm_tensor_t* b, const int32_t* offs,
+                                   int32_t n_groups, const gmm_tensor_t* out, void* stream, uint32_t flags,
+                                   void** scratch_address) {
+  // The scratch need of a launch must fit the fixed array; refuse rather than overrun it.
+  if (kWorkspaceBytes > kStaticScratchBytes) {
+    g_last_cuda_error = "scratch requirement exceeds the 256-byte library-owned scratch";
+    return GMM_ERR_WORKSPACE;
+  }
+  int dev = 0;
+  GMM_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return GMM_ERR_INVALID_ARGUMENT;
+  void* scratch = nullptr;
+  int rc = static_scratch(dev, &scratch);
+  if (rc != GMM_OK) return rc;
+  if (scratch_address) *scratch_address = scratch;
+  // The block keeps whatever the previous call left; the status word has to start at zero.
+  GMM_CUDA_TRY(cudaMemsetAsync(scratch, 0, kStaticScratchBytes, reinterpret_cast<cudaStream_t>(stream)));
+  gmm_launch_t launch;
+  launch.stream = stream;
+  launch.workspace = scratch;
+  launch.workspace_bytes = kStaticScratchBytes;
+  launch.flags = flags;
+  return run(1, a, b, offs, n_groups, out, &launch);
 }
 
 int gmm_select_kernel(int32_t form, const gmm_tensor_t* a, const gmm_tensor_t* b, const gmm_tensor_t* out,

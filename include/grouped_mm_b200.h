@@ -114,6 +114,31 @@ int grouped_mm_3d2d(const gmm_tensor_t* a, const gmm_tensor_t* b, const int32_t*
                     const gmm_tensor_t* out, const gmm_launch_t* launch);
 
 /*
+ * grouped_mm_2d3d() for callers that cannot provide a workspace because they cannot allocate
+ * device memory: code running after an application has handed all device memory to its own
+ * arena, plugin hosts that forbid allocations once initialisation is over, and latency-critical
+ * loops that must never enter the allocator (cudaMalloc and cudaFree also synchronise the whole
+ * device). Same arguments and results as grouped_mm_2d3d(); the 256-byte scratch block (status
+ * word first) lives in a fixed array inside the library image instead, held by every GPU that
+ * loads the library until the process exits. This call allocates nothing and calls no allocating
+ * routine. No counterpart in the reference.
+ *
+ *  - Limit: the scratch is 256 bytes, which covers every problem grouped_mm_2d3d() accepts (the
+ *    scratch need does not grow with the problem); a build whose scratch need exceeded the array
+ *    would return GMM_ERR_WORKSPACE here. The group limit (n_groups <= 1023) is unchanged.
+ *  - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
+ *    that device current). Make that first call before any stream capture is begun.
+ *  - All calls on a device share the one block. Each call clears it on `stream` before launching,
+ *    so nothing from an earlier call leaks in; calls that overlap on the GPU (different streams)
+ *    race on the status word and must be avoided or serialised by the caller.
+ *  - *scratch_address, when not NULL, receives the block's device address, usable as the
+ *    `workspace` argument of gmm_check_status().
+ */
+int grouped_mm_2d3d_static_scratch(const gmm_tensor_t* a, const gmm_tensor_t* b, const int32_t* offs,
+                                   int32_t n_groups, const gmm_tensor_t* out, void* stream, uint32_t flags,
+                                   void** scratch_address);
+
+/*
  * Which kernel the corresponding grouped_mm_* call would use for these arguments (enum
  * gmm_kernel_kind, or a negative gmm_status). `form`: 0 = 3d3d, 1 = 2d3d, 2 = 3d2d, 3 = 2d2d.
  * Launches nothing. No counterpart in the reference, whose kernels take any strides.
