@@ -48,7 +48,7 @@ UNIT = "TFLOP/s"
 
 # DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of the tcgen05 kernel,
 # from an ncu capture; see profiles/. None until captured for that workload.
-NCU_TRAFFIC_BYTES = {}
+NCU_TRAFFIC_BYTES = {"mixtral": 4.979e9}  # profiles/gmm_sm100_pair_kernel_mixtral.md
 
 
 def read_peaks():
@@ -339,7 +339,8 @@ def main():
         "frac_of_sustained_peak": (achieved / peaks["tflops_sustained"]) if peaks["tflops_sustained"] else None,
         "frac_of_nominal_2250": achieved / 2250.0,
         "algorithmic_flops_per_launch": wl.flops, "algorithmic_bytes_per_launch": wl.algorithmic_bytes,
-        "kernel": {1: "gmm_sm100_kernel (TMA + tcgen05)", 2: "gmm_generic_kernel"}.get(kernel, "none"),
+        "kernel": {1: "gmm_sm100_kernel (TMA + tcgen05.mma, one CTA per 128x256 tile)", 2: "gmm_generic_kernel",
+                   3: "gmm_sm100_pair_kernel (TMA + tcgen05.mma.cta_group::2, CTA pair per 256x256 tile)"}.get(kernel, "none"),
     })
 
     # end to end with host buffers

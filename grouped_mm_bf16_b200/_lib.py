@@ -13,7 +13,8 @@ from typing import Optional
 LIB_PATH = Path(__file__).resolve().parent / "lib" / "libgrouped_mm_b200.so"
 
 GMM_BF16, GMM_F16, GMM_F32 = 0, 1, 2
-GMM_KERNEL_NONE, GMM_KERNEL_TCGEN05, GMM_KERNEL_GENERIC = 0, 1, 2
+GMM_KERNEL_NONE, GMM_KERNEL_TCGEN05, GMM_KERNEL_GENERIC, GMM_KERNEL_TCGEN05_PAIR = 0, 1, 2, 3
+TCGEN05_KINDS = (GMM_KERNEL_TCGEN05, GMM_KERNEL_TCGEN05_PAIR)
 GMM_FLAG_FORCE_GENERIC = 0x1
 GMM_ERR_DEVICE_WAIT = -7
 

@@ -112,7 +112,8 @@ def grouped_mm_3d2d(mat_a: torch.Tensor, mat_b: torch.Tensor, offs: torch.Tensor
 
 
 def selected_kernel(form: int, mat_a: torch.Tensor, mat_b: torch.Tensor, out: torch.Tensor) -> int:
-    """Which kernel a call with these tensors is routed to (0 none, 1 tcgen05, 2 generic)."""
+    """Which kernel a call with these tensors is routed to (0 none, 1 tcgen05 single-CTA, 2 generic,
+    3 tcgen05 CTA-pair)."""
     lib = _lib.load()
     a, b, c = _desc(mat_a), _desc(mat_b), _desc(out)
     rc = lib.gmm_select_kernel(form, ctypes.byref(a), ctypes.byref(b), ctypes.byref(c), _flags())

@@ -530,7 +530,9 @@ int gmm_select_kernel(int32_t form, const gmm_tensor_t* a, const gmm_tensor_t* b
   if (rc != GMM_OK) return rc;
   if (nothing) return GMM_KERNEL_NONE;
   if (flags & GMM_FLAG_FORCE_GENERIC) return GMM_KERNEL_GENERIC;
-  return plan_fast(p, flags).ok ? GMM_KERNEL_TCGEN05 : GMM_KERNEL_GENERIC;
+  const FastPlan plan = plan_fast(p, flags);
+  if (!plan.ok) return GMM_KERNEL_GENERIC;
+  return plan.pair ? GMM_KERNEL_TCGEN05_PAIR : GMM_KERNEL_TCGEN05;
 }
 
 int gmm_check_status(void* workspace, void* stream, int32_t* raw) {

@@ -41,8 +41,9 @@ enum gmm_status {
 /* Which kernel a call is routed to. */
 enum gmm_kernel_kind {
   GMM_KERNEL_NONE = 0,    /* nothing to launch (empty problem) */
-  GMM_KERNEL_TCGEN05 = 1, /* TMA + tcgen05.mma persistent kernel */
-  GMM_KERNEL_GENERIC = 2  /* any-stride fp32-FMA kernel */
+  GMM_KERNEL_TCGEN05 = 1,      /* TMA + tcgen05.mma persistent kernel, one CTA per 128 x 256 tile */
+  GMM_KERNEL_GENERIC = 2,      /* any-stride fp32-FMA kernel */
+  GMM_KERNEL_TCGEN05_PAIR = 3  /* TMA + tcgen05.mma.cta_group::2 kernel, a CTA pair per 256 x 256 tile */
 };
 
 /* Flags for gmm_launch_t.flags. */
