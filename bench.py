@@ -291,6 +291,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="mixtral",
                     choices=["mixtral", "deepseek_up", "deepseek_down", "batched", "wgrad"])
+    ap.add_argument("--dims-scale", type=float, default=1.0,
+                    help="shrink the fixed dimensions (K, N, M) of the workload; for small profiling cases only")
+    ap.add_argument("--rows-scale", type=float, default=1.0,
+                    help="shrink the ragged extent (routed rows) of the workload; for small profiling cases only")
     ap.add_argument("--no-baselines", action="store_true", help="skip the CPU and Triton baseline legs")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -305,7 +309,7 @@ def main():
     peaks = read_peaks()
 
     # Every rank owns its own experts (weak scaling): same shape, its own seeded draw.
-    wl = make_workload(args.workload, dev, seed=rank)
+    wl = make_workload(args.workload, dev, seed=rank, scale=args.rows_scale, dims_scale=args.dims_scale)
     from grouped_mm_bf16_b200 import _lib, _op
 
     out = call_operator(wl)
@@ -400,6 +404,8 @@ def main():
                             f"{len(wl.sizes) if wl.sizes else wl.mat_a.size(0)} groups per GPU, seeded sizes",
                 "sharding": "expert-parallel, one process per GPU, no collective in the timed region",
                 "l2": "inputs larger than L2 (no flush needed)",
+                "reduced": None if (args.dims_scale == 1.0 and args.rows_scale == 1.0) else
+                f"NOT the benchmark size: dims x{args.dims_scale}, rows x{args.rows_scale} (profiling case)",
             },
             "roofline": roofline, "e2e": e2e, "gpu_launches": args.steps, "clocks": sampler.summary(),
             "device_status": status,
