@@ -6,11 +6,13 @@ There is no fallback: if the library is missing or a call fails, a RuntimeError 
 from __future__ import annotations
 
 import ctypes
+import os
 import threading
 from pathlib import Path
 from typing import Optional
 
-LIB_PATH = Path(__file__).resolve().parent / "lib" / "libgrouped_mm_b200.so"
+# GROUPED_MM_B200_LIB points at another build of the library (for example to compare two builds).
+LIB_PATH = Path(os.environ.get("GROUPED_MM_B200_LIB") or Path(__file__).resolve().parent / "lib" / "libgrouped_mm_b200.so")
 
 GMM_BF16, GMM_F16, GMM_F32 = 0, 1, 2
 GMM_KERNEL_NONE, GMM_KERNEL_TCGEN05, GMM_KERNEL_GENERIC, GMM_KERNEL_TCGEN05_PAIR = 0, 1, 2, 3

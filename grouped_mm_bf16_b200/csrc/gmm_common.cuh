@@ -189,4 +189,13 @@ __device__ __forceinline__ TileInfo decode_tile(const CanonProblem& p, const Sch
   return ti;
 }
 
+// Contraction length of tile `t` without the full decode: all the MMA issuer needs. It is a
+// constant except in KRAGGED mode, where it is the length of the tile's group.
+__device__ __forceinline__ int tile_klen(const CanonProblem& p, const SchedSmem& s, int t) {
+  if (p.mode != MODE_KRAGGED) return p.K;
+  const int g = t / (s.m_tiles * s.n_tiles);
+  const int len = s.ends[g] - (g ? s.ends[g - 1] : 0);
+  return len > 0 ? len : 0;
+}
+
 }  // namespace gmm

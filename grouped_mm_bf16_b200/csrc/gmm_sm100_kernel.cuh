@@ -308,8 +308,8 @@ gmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     int it = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < total && ok; t += gridDim.x, ++it) {
-      const TileInfo ti = decode_tile<kBM, kBN>(p, tail.sched, t);
-      const int nkb = (ti.klen + kBK - 1) / kBK;
+      const int klen = tile_klen(p, tail.sched, t);  // the issuer needs no tile coordinates
+      const int nkb = (klen + kBK - 1) / kBK;
       const int buf = it & 1;
       const uint32_t aph = (it >> 1) & 1;
       if (!mbar_wait(&tail.acc_empty[buf], aph ^ 1, abort_flag)) {
@@ -332,7 +332,7 @@ gmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           // The last k-block of a group over-reads k-rows of the next group. Both operands are
           // MN-major here, so k-rows are whole 128-byte lines: rows [r, 64) of every chunk form
           // one contiguous range, zeroed before the MMA so they contribute exactly 0.
-          const int r = ti.klen - kb * kBK;
+          const int r = klen - kb * kBK;
           if (r < kBK) {
             const int n16 = (kBK - r) * 8;  // 16-byte words per chunk
             const uint4 z = make_uint4(0, 0, 0, 0);

@@ -144,9 +144,8 @@ gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       uint32_t ph = 0;
       int it = 0;
       bool ok = true;
+      const int nkb = (p.K + kBK - 1) / kBK;  // same for every tile: this kernel has no K-ragged mode
       for (int t = pair; t < total && ok; t += n_pairs, ++it) {
-        const TileInfo ti = decode_tile<kPairBM, kBN>(p, tail.sched, t);
-        const int nkb = (ti.klen + kBK - 1) / kBK;
         const int buf = it & 1;
         const uint32_t aph = (it >> 1) & 1;
         if (!mbar_wait(&tail.acc_empty[buf], aph ^ 1, abort_flag)) {
