@@ -80,9 +80,12 @@ int init_device(int dev) {
     if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_kernel<true, __nv_bfloat16>);
     if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_kernel<true, __half>);
     if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_kernel<true, float>);
-    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_pair_kernel<__nv_bfloat16>, kPairSmemBytes);
-    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_pair_kernel<__half>, kPairSmemBytes);
-    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_pair_kernel<float>, kPairSmemBytes);
+    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_pair_kernel<false, __nv_bfloat16>, kPairSmemBytes);
+    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_pair_kernel<false, __half>, kPairSmemBytes);
+    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_pair_kernel<false, float>, kPairSmemBytes);
+    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_pair_kernel<true, __nv_bfloat16>, kPairSmemBytes);
+    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_pair_kernel<true, __half>, kPairSmemBytes);
+    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_pair_kernel<true, float>, kPairSmemBytes);
     d.status = rc;
   });
   return d.status;
@@ -224,7 +227,7 @@ FastPlan plan_fast(const CanonProblem& p, uint32_t flags) {
   f.ok = true;
   // 256-row pair tiles pay off when groups are tall (little tail waste) and N spans both halves.
   // The group sizes live on the device, so the host decides on the mean rows per group.
-  if (p.mode != MODE_KRAGGED && p.N > kPairBNHalf) {
+  if (p.N > kPairBNHalf) {
     const long long mean_rows = (p.mode == MODE_MRAGGED) ? (long long)p.M / (p.G > 0 ? p.G : 1) : p.M;
     f.pair = mean_rows >= 768;
     if (flags & GMM_FLAG_FORCE_PAIR) f.pair = true;
@@ -328,7 +331,10 @@ int launch_fast_kr(const CUtensorMap& ta, const CUtensorMap& tb, const FastParam
 
 template <typename TOut>
 int launch_pair_t(const CUtensorMap& ta, const CUtensorMap& tb, const FastParams& fp, int grid, cudaStream_t st) {
-  gmm_sm100_pair_kernel<TOut><<<grid, kFastThreads, kPairSmemBytes, st>>>(ta, tb, fp);
+  if (fp.p.mode == MODE_KRAGGED)
+    gmm_sm100_pair_kernel<true, TOut><<<grid, kFastThreads, kPairSmemBytes, st>>>(ta, tb, fp);
+  else
+    gmm_sm100_pair_kernel<false, TOut><<<grid, kFastThreads, kPairSmemBytes, st>>>(ta, tb, fp);
   GMM_CUDA_TRY(cudaGetLastError());
   return GMM_OK;
 }

@@ -59,7 +59,10 @@ struct SchedSmem {
   int n_tiles;
   int total;                   // total tiles
   int panel;                   // n-tiles per B panel
+  short order[kMaxGroups];     // KRAGGED: groups by decreasing contraction length (see sched_init)
 };
+
+constexpr int kSortGroupsMax = 256;  // above this many groups the K-ragged order is left as given
 
 constexpr int kDefaultPanel = 16;
 
@@ -93,6 +96,20 @@ __device__ __forceinline__ void sched_init(const CanonProblem& p, SchedSmem& s) 
       s.n_tiles = n_tiles;
       s.mt_total = s.m_tiles * p.G;
       s.total = s.mt_total * n_tiles;
+    }
+    // A tile's cost is its group's contraction length, which varies widely between groups, while
+    // tiles are dealt to CTAs round-robin. Dealing them in order of decreasing cost (and reversing
+    // every other round, see tile_of_round) keeps the CTAs' totals within a few percent of each
+    // other. Rank by counting: O(G^2 / threads), done only for moderate G.
+    for (int g = tid; g < p.G; g += nthr) {
+      if (p.G > kSortGroupsMax) { s.order[g] = (short)g; continue; }
+      const int len = max(0, s.ends[g] - (g ? s.ends[g - 1] : 0));
+      int rank = 0;
+      for (int j = 0; j < p.G; ++j) {
+        const int lj = max(0, s.ends[j] - (j ? s.ends[j - 1] : 0));
+        rank += (lj > len) || (lj == len && j < g);
+      }
+      s.order[rank] = (short)g;
     }
     __syncthreads();
     return;
@@ -155,8 +172,9 @@ __device__ __forceinline__ TileInfo decode_tile(const CanonProblem& p, const Sch
     start = g ? s.ends[g - 1] : 0;
   } else {
     const int per_group = s.m_tiles * s.n_tiles;
-    g = t / per_group;
-    idx = t - g * per_group;
+    const int gpos = t / per_group;
+    idx = t - gpos * per_group;
+    g = (p.mode == MODE_KRAGGED) ? (int)s.order[gpos] : gpos;
     mt_g = s.m_tiles;
   }
   const int panel_tiles = mt_g * s.panel;
@@ -189,11 +207,19 @@ __device__ __forceinline__ TileInfo decode_tile(const CanonProblem& p, const Sch
   return ti;
 }
 
+// Tile taken by work unit `unit` (a CTA or a CTA pair) of `units` in round `round`. With SNAKE the
+// odd rounds run backwards, which evens out a cost-sorted tile sequence (K-ragged mode).
+template <bool SNAKE>
+__device__ __forceinline__ int tile_of_round(int round, int unit, int units) {
+  if (SNAKE && (round & 1)) return round * units + (units - 1 - unit);
+  return round * units + unit;
+}
+
 // Contraction length of tile `t` without the full decode: all the MMA issuer needs. It is a
 // constant except in KRAGGED mode, where it is the length of the tile's group.
 __device__ __forceinline__ int tile_klen(const CanonProblem& p, const SchedSmem& s, int t) {
   if (p.mode != MODE_KRAGGED) return p.K;
-  const int g = t / (s.m_tiles * s.n_tiles);
+  const int g = s.order[t / (s.m_tiles * s.n_tiles)];
   const int len = s.ends[g] - (g ? s.ends[g - 1] : 0);
   return len > 0 ? len : 0;
 }

@@ -251,7 +251,9 @@ gmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+      for (int round = 0; ok; ++round) {
+        const int t = tile_of_round<KRAGGED>(round, blockIdx.x, gridDim.x);
+        if (t >= total) break;
         const TileInfo ti = decode_tile<kBM, kBN>(p, tail.sched, t);
         const int nkb = (ti.klen + kBK - 1) / kBK;
         const int az = a_batched ? ti.g : 0;
@@ -307,7 +309,9 @@ gmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     uint32_t ph = 0;
     int it = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < total && ok; t += gridDim.x, ++it) {
+    for (; ok; ++it) {
+      const int t = tile_of_round<KRAGGED>(it, blockIdx.x, gridDim.x);
+      if (t >= total) break;
       const int klen = tile_klen(p, tail.sched, t);  // the issuer needs no tile coordinates
       const int nkb = (klen + kBK - 1) / kBK;
       const int buf = it & 1;
@@ -372,7 +376,9 @@ gmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     TOut* c_base = reinterpret_cast<TOut*>(p.c);
     int it = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < total && ok; t += gridDim.x, ++it) {
+    for (; ok; ++it) {
+      const int t = tile_of_round<KRAGGED>(it, blockIdx.x, gridDim.x);
+      if (t >= total) break;
       const TileInfo ti = decode_tile<kBM, kBN>(p, tail.sched, t);
       const int buf = it & 1;
       const uint32_t aph = (it >> 1) & 1;

@@ -1,4 +1,4 @@
-// CTA-pair variant of the persistent grouped GEMM for sm_100a (UNIFORM and MRAGGED modes).
+// CTA-pair variant of the persistent grouped GEMM for sm_100a (all three modes).
 //
 // Two CTAs on the two SMs of one TPC (a cluster of 2) share every 256 x 256 output tile:
 // CTA r loads rows [128 r, 128 r + 128) of the A tile and columns [128 r, 128 r + 128) of the B
@@ -13,6 +13,13 @@
 //   empty[s]     one per CTA; the leader's tcgen05.commit arrives on both
 //   acc_full[b]  one per CTA; same
 //   acc_empty[b] lives in the leader; the 2 x 128 epilogue threads arrive on it
+//
+// K-ragged mode (KRAGGED = true) differs in one respect. The last k-block of a group over-reads
+// k-rows of the next group, and both CTAs have to zero those rows of their own stage before the
+// MMA may read them. So each CTA's loads credit its OWN full[s]; warp 1 of the peer CTA (idle
+// otherwise) waits for its stage, zeroes the tail rows if there are any, and then arrives on
+// peer_ready[s] in the leader; the leader's issuer waits for its own full[s], zeroes its own tail,
+// waits for peer_ready[s] and only then issues.
 #pragma once
 
 #include "gmm_sm100_kernel.cuh"
@@ -31,6 +38,7 @@ struct PairSmemTail {
   uint64_t empty[kPairStages];
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
+  uint64_t peer_ready[kPairStages];  // K-ragged mode only: the peer's stage is loaded and its tail zeroed
   uint32_t tmem_base;
   int abort_flag;
   SchedSmem sched;
@@ -43,9 +51,22 @@ enum PairStatus : int {
   ST_PAIR_PRODUCER_TIMEOUT = 0x201,
   ST_PAIR_MMA_TIMEOUT = 0x202,
   ST_PAIR_EPILOGUE_TIMEOUT = 0x203,
+  ST_PAIR_RELAY_TIMEOUT = 0x204,
 };
 
-template <typename TOut>
+// Zeroes k-rows [r, 64) of `chunks` MN-major chunks (each [64 k-rows][128 B]) of one stage buffer.
+// Whole-warp call; ends with the proxy fence that makes the zeros visible to the MMA.
+__device__ __forceinline__ void zero_tail_rows(uint8_t* stage_buf, int chunks, int r, int lane) {
+  const int n16 = (kBK - r) * 8;  // 16-byte words per chunk
+  const uint4 z = make_uint4(0, 0, 0, 0);
+  for (int c = 0; c < chunks; ++c) {
+    uint4* q = reinterpret_cast<uint4*>(stage_buf + c * kChunkBytes + r * 128);
+    for (int i = lane; i < n16; i += 32) q[i] = z;
+  }
+  fence_proxy_async_smem();
+}
+
+template <bool KRAGGED, typename TOut>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFastThreads, 1)
 gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                       const FastParams fp) {
@@ -68,6 +89,7 @@ gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     for (int s = 0; s < kPairStages; ++s) {
       mbar_init(&tail.full[s], 1);
       mbar_init(&tail.empty[s], 1);
+      mbar_init(&tail.peer_ready[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tail.acc_full[b], 1);
@@ -98,10 +120,13 @@ gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
-      for (int t = pair; t < total && ok; t += n_pairs) {
+      for (int round = 0; ok; ++round) {
+        const int t = tile_of_round<KRAGGED>(round, pair, n_pairs);
+        if (t >= total) break;
         const TileInfo ti = decode_tile<kPairBM, kBN>(p, tail.sched, t);
         const int nkb = (ti.klen + kBK - 1) / kBK;
         const int az = a_batched ? ti.g : 0;
+        const int bz = KRAGGED ? 0 : ti.g;
         const int row0 = ti.m0 + int(rank) * 128;
         const int col0 = ti.n0 + int(rank) * kPairBNHalf;
         for (int kb = 0; kb < nkb; ++kb) {
@@ -110,13 +135,19 @@ gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             ok = false;
             break;
           }
-          if (rank == 0) mbar_arrive_expect_tx(&tail.full[s], 2 * kPairStageBytes);
-          const uint32_t full_leader = map_to_cta(smem_u32(&tail.full[s]), 0);
-          const int k = kb * kBK;
+          uint32_t bar;  // where this CTA's loads are credited
+          if constexpr (KRAGGED) {
+            mbar_arrive_expect_tx(&tail.full[s], kPairStageBytes);
+            bar = smem_u32(&tail.full[s]);
+          } else {
+            if (rank == 0) mbar_arrive_expect_tx(&tail.full[s], 2 * kPairStageBytes);
+            bar = map_to_cta(smem_u32(&tail.full[s]), 0);
+          }
+          const int k = ti.k0 + kb * kBK;
           uint8_t* sa = smem_a + s * kPairAStageBytes;
           uint8_t* sb = smem_b + s * kPairBStageBytes;
-          auto load_a = [&](void* dst, int x, int y) { tma_load_3d_pair(dst, &tmap_a, full_leader, x, y, az); };
-          auto load_b = [&](void* dst, int x, int y) { tma_load_3d_pair(dst, &tmap_b, full_leader, x, y, ti.g); };
+          auto load_a = [&](void* dst, int x, int y) { tma_load_3d_pair(dst, &tmap_a, bar, x, y, az); };
+          auto load_b = [&](void* dst, int x, int y) { tma_load_3d_pair(dst, &tmap_b, bar, x, y, bz); };
           if (!fp.a_mn) {
             load_a(sa, k, row0);
           } else {
@@ -144,11 +175,14 @@ gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       uint32_t ph = 0;
       int it = 0;
       bool ok = true;
-      const int nkb = (p.K + kBK - 1) / kBK;  // same for every tile: this kernel has no K-ragged mode
-      for (int t = pair; t < total && ok; t += n_pairs, ++it) {
+      for (; ok; ++it) {
+        const int t = tile_of_round<KRAGGED>(it, pair, n_pairs);
+        if (t >= total) break;
+        const int klen = tile_klen(p, tail.sched, t);  // the issuer needs no tile coordinates
+        const int nkb = (klen + kBK - 1) / kBK;
         const int buf = it & 1;
         const uint32_t aph = (it >> 1) & 1;
-        if (!mbar_wait(&tail.acc_empty[buf], aph ^ 1, abort_flag)) {
+        if (!mbar_wait_cluster(&tail.acc_empty[buf], aph ^ 1, abort_flag)) {
           if (lane == 0) atomicCAS(p.status, 0, ST_PAIR_MMA_TIMEOUT);
           ok = false;
           break;
@@ -160,6 +194,19 @@ gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             if (lane == 0) atomicCAS(p.status, 0, ST_PAIR_MMA_TIMEOUT + 0x10);
             ok = false;
             break;
+          }
+          if constexpr (KRAGGED) {
+            const int r = klen - kb * kBK;
+            if (r < kBK) {
+              zero_tail_rows(smem_a + s * kPairAStageBytes, 2, r, lane);
+              zero_tail_rows(smem_b + s * kPairBStageBytes, 2, r, lane);
+            }
+            __syncwarp();
+            if (!mbar_wait_cluster(&tail.peer_ready[s], ph, abort_flag)) {
+              if (lane == 0) atomicCAS(p.status, 0, ST_PAIR_MMA_TIMEOUT + 0x20);
+              ok = false;
+              break;
+            }
           }
           tcgen05_fence_after_sync();
           if (lane == 0) {
@@ -178,6 +225,36 @@ gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         if (ok && lane == 0) umma_commit_pair(&tail.acc_full[buf], 0x3);
         __syncwarp();
       }
+    } else if constexpr (KRAGGED) {
+      // -------------------------------------------------------- relay (peer CTA, K-ragged mode)
+      const uint32_t ready_leader0 = map_to_cta(smem_u32(&tail.peer_ready[0]), 0);
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int round = 0; ok; ++round) {
+        const int t = tile_of_round<KRAGGED>(round, pair, n_pairs);
+        if (t >= total) break;
+        const int klen = tile_klen(p, tail.sched, t);
+        const int nkb = (klen + kBK - 1) / kBK;
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!mbar_wait(&tail.full[s], ph, abort_flag)) {
+            if (lane == 0) atomicCAS(p.status, 0, ST_PAIR_RELAY_TIMEOUT);
+            ok = false;
+            break;
+          }
+          const int r = klen - kb * kBK;
+          if (r < kBK) {
+            zero_tail_rows(smem_a + s * kPairAStageBytes, 2, r, lane);
+            zero_tail_rows(smem_b + s * kPairBStageBytes, 2, r, lane);
+          }
+          __syncwarp();
+          if (lane == 0) {
+            if (r < kBK) mbar_arrive_cluster(ready_leader0 + s * (uint32_t)sizeof(uint64_t));
+            else mbar_arrive_cluster_relaxed(ready_leader0 + s * (uint32_t)sizeof(uint64_t));
+          }
+          if (++s == kPairStages) { s = 0; ph ^= 1; }
+        }
+      }
     }
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5 of both CTAs)
@@ -185,7 +262,9 @@ gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     TOut* c_base = reinterpret_cast<TOut*>(p.c);
     int it = 0;
     bool ok = true;
-    for (int t = pair; t < total && ok; t += n_pairs, ++it) {
+    for (; ok; ++it) {
+      const int t = tile_of_round<KRAGGED>(it, pair, n_pairs);
+      if (t >= total) break;
       const TileInfo ti = decode_tile<kPairBM, kBN>(p, tail.sched, t);
       const int buf = it & 1;
       const uint32_t aph = (it >> 1) & 1;
@@ -203,7 +282,7 @@ gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       // A warp whose rows lie wholly past the group's end has nothing to read or store.
       if (row0 < ti.rows)
         epilogue_store_warp<TOut>(t_row, c_warp, p.c_sm, p.c_sn, ti.rows - row0, ncols_tile,
-                                  epi_stage + (warp - 2) * kWarpStageBytes, false, lane);
+                                  epi_stage + (warp - 2) * kWarpStageBytes, KRAGGED && ti.klen == 0, lane);
       tcgen05_fence_before_sync();
       mbar_arrive_cluster(map_to_cta(smem_u32(&tail.acc_empty[buf]), 0));
     }

@@ -182,7 +182,7 @@ K_PATTERNS = [[64, 64], [8, 0, 16, 24, 8], [7, 0, 1, 13, 11], [63, 65, 1, 127], 
 @pytest.mark.parametrize("sizes", K_PATTERNS)
 @pytest.mark.parametrize("m,n", [(16, 24), (136, 264), (128, 256)])
 @pytest.mark.parametrize("out_dtype", [None, torch.float32])
-def test_2d2d_k_ragged_tcgen05(sizes, m, n, out_dtype):
+def test_2d2d_k_ragged_tcgen05(sizes, m, n, out_dtype, tile_kernel):
     g = torch.Generator(device=DEV).manual_seed(sum(sizes) + m)
     kt = sum(sizes)
     a = torch.randn((kt, m), device=DEV, generator=g).bfloat16().t()  # column-major [M, K_total]
@@ -236,7 +236,7 @@ def test_fp32_inputs_are_true_fp32():
 
 @pytest.mark.parametrize("form", ["2d3d", "3d2d", "2d2d"])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_1023_groups(form, dtype):
+def test_1023_groups(form, dtype, tile_kernel):
     """Alternating one-element and empty groups with a trailing empty group
     (the reference's large-group-count cases, tests/test_grouped_mm.py:661-747)."""
     sizes = [1 if i % 2 == 0 else 0 for i in range(1023)]
@@ -427,7 +427,7 @@ def test_wgrad_full_size_groups_and_checksum():
     assert wl.mat_a.shape == (4096, 65536) and wl.mat_a.stride() == (1, 4096)
     out = grouped_mm(wl.mat_a, wl.mat_b, offs=wl.offs, out_dtype=torch.float32)
     assert out.dtype == torch.float32 and out.shape == (64, 4096, 1536)
-    assert _op.selected_kernel(_lib.FORM_2D2D, wl.mat_a, wl.mat_b, out) == _lib.GMM_KERNEL_TCGEN05
+    assert _op.selected_kernel(_lib.FORM_2D2D, wl.mat_a, wl.mat_b, out) == _lib.GMM_KERNEL_TCGEN05_PAIR
     bounds = group_bounds(wl.offs.cpu(), 65536)
     empties = [g for g, (s, e) in enumerate(bounds) if e == s]
     assert empties, "the seeded draw has empty groups"
