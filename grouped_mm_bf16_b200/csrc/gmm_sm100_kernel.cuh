@@ -6,8 +6,9 @@
 //
 // Each CTA owns 512 TMEM columns = two 128 x 256 fp32 accumulators, so the epilogue of tile i
 // overlaps the main loop of tile i+1. Tiles are (group, m-tile, n-tile) items decoded on the
-// device from `offs` (gmm_common.cuh); every role walks the same sequence
-// blockIdx.x, blockIdx.x + gridDim.x, ...
+// device from `offs` (gmm_common.cuh); every role walks the same sequence of tiles, one per
+// round (tile_of_round): blockIdx.x, blockIdx.x + gridDim.x, ... and, in K-ragged mode where
+// tiles are sorted by cost, every other round backwards.
 //
 // Replaces the reference's Triton kernels for the same math: kernels.py:197-245 (3D x 3D),
 // kernels.py:304-419 (2D x 3D main + prologue pair) and kernels.py:248-301 (2D x 2D), all of
@@ -46,9 +47,15 @@ struct FastSmemTail {
   SchedSmem sched;
 };
 
-constexpr int kStageRowBytesFwd = 144;  // see kStageRowBytes below
+// Per-warp staging area used to turn "one thread = one output row" (the TMEM read layout) into
+// row-contiguous global stores: 32 rows of 128 bytes, padded to 144 so that both the row-wise
+// writes and the transposed reads are free of bank conflicts.
+constexpr int kStageRowBytes = 144;
+constexpr int kWarpStageBytes = 32 * kStageRowBytes;
+constexpr int kEpilogueStageBytes = 4 * kWarpStageBytes;
+
 constexpr size_t kFastSmemBytes =
-    1024 /*alignment slack*/ + size_t(kStages) * kStageBytes + sizeof(FastSmemTail) + 4 * 32 * kStageRowBytesFwd;
+    1024 /*alignment slack*/ + size_t(kStages) * kStageBytes + sizeof(FastSmemTail) + kEpilogueStageBytes;
 
 struct FastParams {
   CanonProblem p;
@@ -117,13 +124,6 @@ __device__ __forceinline__ void store_row_chunk(TOut* dst, long long col_stride,
     }
   }
 }
-
-// Per-warp staging area used to turn "one thread = one output row" (the TMEM read layout) into
-// row-contiguous global stores: 32 rows of 128 bytes, padded to 144 so that both the row-wise
-// writes and the transposed reads are free of bank conflicts.
-constexpr int kStageRowBytes = 144;
-constexpr int kWarpStageBytes = 32 * kStageRowBytes;
-constexpr int kEpilogueStageBytes = 4 * kWarpStageBytes;
 
 // Stores this warp's 32 rows of one accumulator tile. `t_row` is the TMEM address of the warp's
 // lane quarter at column 0 of the tile, `c_warp` points at (first row of the warp, first column of
