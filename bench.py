@@ -280,6 +280,21 @@ def triton_reference_tflops(wl, steps: int, warmup: int):
         return {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
 
 
+def training_step_tflops(op, wl, steps: int, warmup: int):
+    """Forward + both gradients of the workload through autograd (3x the forward FLOPs)."""
+    a = wl.mat_a.detach().clone().requires_grad_(True)
+    b = wl.mat_b.detach().clone().requires_grad_(True)
+    cot = torch.ones_like(op(a, b, offs=wl.offs)).detach()
+
+    def step():
+        out = op(a, b, offs=wl.offs)
+        torch.autograd.grad(out, [a, b], cot)
+
+    ms = time_steps(None, step, steps, warmup) / steps
+    return {"value": 3.0 * wl.flops / (ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms, "steps": steps,
+            "what": "forward + dA + dB per step, 3x the forward FLOPs"}
+
+
 # ----------------------------------------------------------------------------- main arm
 
 
@@ -419,6 +434,15 @@ def main():
             line["cpu_baseline"] = {"value": f / dt / 1e12, "unit": UNIT, "cores": os.cpu_count() or 1,
                                     "kind": "port", "sample": desc}
             line["triton_reference"] = triton_reference_tflops(wl, max(3, min(args.steps, 20)), 3)
+            if wl.form == "2d3d":
+                from grouped_mm_bf16_b200 import grouped_mm
+
+                try:
+                    # No Triton leg here: the reference's backward kernels did not finish one Mixtral-shape
+                    # step within four minutes on a B200, so they are not run inside the benchmark.
+                    line["training_step"] = training_step_tflops(grouped_mm, wl, max(3, min(args.steps, 20)), 3)
+                except Exception as exc:  # informative legs must not hide the headline number
+                    line["training_step_error"] = f"{type(exc).__name__}: {exc}"[:200]
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()

@@ -59,7 +59,12 @@ def _launch(form: int, mat_a: torch.Tensor, mat_b: torch.Tensor, offs: Optional[
     if not (mat_a.is_cuda and mat_b.is_cuda and out.is_cuda):
         raise RuntimeError("grouped_mm_b200 is GPU-only; CPU tensors are not supported")
     dev = mat_a.device
-    with torch.cuda.device(dev):
+    # The library launches on the current device: switch only when the tensors live elsewhere.
+    switch = dev.index is not None and dev.index != torch.cuda.current_device()
+    if switch:
+        prev = torch.cuda.current_device()
+        torch.cuda.set_device(dev)
+    try:
         ws = workspace(dev)
         launch = _lib.GmmLaunch()
         launch.stream = torch.cuda.current_stream(dev).cuda_stream
@@ -70,10 +75,13 @@ def _launch(form: int, mat_a: torch.Tensor, mat_b: torch.Tensor, offs: Optional[
         if form == _lib.FORM_3D3D:
             rc = lib.grouped_mm_3d3d(ctypes.byref(a), ctypes.byref(b), ctypes.byref(c), ctypes.byref(launch))
         else:
-            fn = {_lib.FORM_2D3D: lib.grouped_mm_2d3d, _lib.FORM_3D2D: lib.grouped_mm_3d2d,
-                  _lib.FORM_2D2D: lib.grouped_mm_2d2d}[form]
-            rc = fn(ctypes.byref(a), ctypes.byref(b), ctypes.c_void_p(offs.data_ptr()), int(offs.numel()),
-                    ctypes.byref(c), ctypes.byref(launch))
+            fn = (lib.grouped_mm_2d3d if form == _lib.FORM_2D3D else
+                  lib.grouped_mm_3d2d if form == _lib.FORM_3D2D else lib.grouped_mm_2d2d)
+            rc = fn(ctypes.byref(a), ctypes.byref(b), offs.data_ptr(), offs.numel(), ctypes.byref(c),
+                    ctypes.byref(launch))
+    finally:
+        if switch:
+            torch.cuda.set_device(prev)
     if rc != 0:
         raise RuntimeError(_lib.error_message(lib, rc))
 
@@ -89,26 +97,35 @@ def _(mat_a, mat_b, offs, out, form):
     return None
 
 
+def _dispatch(form: int, mat_a, mat_b, offs, out) -> None:
+    """Eager calls go straight to the library; under torch.compile the registered custom op is
+    used so that the call is traceable (the op's dispatcher round trip costs ~15 us per call)."""
+    if torch.compiler.is_compiling():
+        _forward_op(mat_a, mat_b, offs, out, form)
+    else:
+        _launch(form, mat_a, mat_b, offs, out)
+
+
 def grouped_mm_3d3d(mat_a: torch.Tensor, mat_b: torch.Tensor, out: torch.Tensor) -> None:
     """out[g] = mat_a[g] @ mat_b[g] (reference: kernels.py:524-550)."""
-    _forward_op(mat_a, mat_b, None, out, _lib.FORM_3D3D)
+    _dispatch(_lib.FORM_3D3D, mat_a, mat_b, None, out)
 
 
 def grouped_mm_2d2d(mat_a: torch.Tensor, mat_b: torch.Tensor, offs: torch.Tensor, out: torch.Tensor) -> None:
     """out[g] = mat_a[:, ks:ke] @ mat_b[ks:ke, :], zeros for an empty range (reference: kernels.py:553-580)."""
-    _forward_op(mat_a, mat_b, offs, out, _lib.FORM_2D2D)
+    _dispatch(_lib.FORM_2D2D, mat_a, mat_b, offs, out)
 
 
 def grouped_mm_2d3d(mat_a: torch.Tensor, mat_b: torch.Tensor, offs: torch.Tensor, out: torch.Tensor) -> None:
     """out[rows_g] = mat_a[rows_g] @ mat_b[g] (reference: kernels.py:583-686)."""
-    _forward_op(mat_a, mat_b, offs, out, _lib.FORM_2D3D)
+    _dispatch(_lib.FORM_2D3D, mat_a, mat_b, offs, out)
 
 
 def grouped_mm_3d2d(mat_a: torch.Tensor, mat_b: torch.Tensor, offs: torch.Tensor, out: torch.Tensor) -> None:
     """out[:, cols_g] = mat_a[g] @ mat_b[:, cols_g] (reference: kernels.py:689-717)."""
     if mat_a.size(0) != offs.numel():
         raise RuntimeError("matrix batch sizes have to match")
-    _forward_op(mat_a, mat_b, offs, out, _lib.FORM_3D2D)
+    _dispatch(_lib.FORM_3D2D, mat_a, mat_b, offs, out)
 
 
 def selected_kernel(form: int, mat_a: torch.Tensor, mat_b: torch.Tensor, out: torch.Tensor) -> int:

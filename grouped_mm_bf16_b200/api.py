@@ -142,7 +142,7 @@ def output_geometry(a_shape: Sequence[int], b_shape: Sequence[int], n_groups: Op
 
 
 def create_output(mat_a, mat_b, offs, out_dtype: torch.dtype) -> torch.Tensor:
-    esize = torch.empty((), dtype=out_dtype).element_size()
+    esize = out_dtype.itemsize
     size, strides = output_geometry(tuple(mat_a.shape), tuple(mat_b.shape),
                                     None if offs is None else offs.size(0), esize)
     return torch.empty_strided(size, strides, device=mat_a.device, dtype=out_dtype)

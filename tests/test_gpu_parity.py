@@ -260,6 +260,16 @@ def test_1023_groups(form, dtype, tile_kernel):
         _assert_parity(a, b, offs, 1.0, 1.0)
 
 
+def test_registered_torch_custom_op():
+    """The op registered with torch.library (the traceable entry used under torch.compile) gives
+    the same bits as the eager path, which calls the same launcher directly."""
+    wl = make_workload("mixtral", DEV, seed=2, scale=1 / 32, dims_scale=1 / 8)
+    want = grouped_mm(wl.mat_a, wl.mat_b, offs=wl.offs)
+    got = torch.empty_like(want)
+    assert torch.ops.grouped_mm_b200.forward(wl.mat_a, wl.mat_b, wl.offs, got, _lib.FORM_2D3D) is None
+    assert torch.equal(got, want)
+
+
 # ----------------------------------------------------------------------------- what must not be written
 
 
