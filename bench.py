@@ -193,7 +193,7 @@ def call_operator(wl):
 # ----------------------------------------------------------------------------- CPU baseline (oracle)
 
 
-def cpu_oracle_sample(a_cpu, b_cpu, sizes, budget_s: float):
+def cpu_oracle_sample(a_cpu, b_cpu, sizes, budget_s: float, workload_rows=None):
     """Per-group fp32 matmul on CPU tensors over a bounded prefix of every group's rows.
 
     Returns (flops done, seconds, description). Rows are taken group by group in chunks until the
@@ -224,7 +224,8 @@ def cpu_oracle_sample(a_cpu, b_cpu, sizes, budget_s: float):
     grouped_mm_oracle(a_s, b_s, offs_s)
     dt = time.perf_counter() - t0
     rows = int(a_s.size(0))
-    return 2.0 * rows * k * n, dt, f"first {rows} of {sum(sizes)} rows ({rows // len(live)} per group, {len(live)} groups), K={k}, N={n}"
+    of = workload_rows if workload_rows is not None else sum(sizes)
+    return 2.0 * rows * k * n, dt, f"first {rows} of {of} rows ({rows // len(live)} per group, {len(live)} groups), K={k}, N={n}"
 
 
 def run_reference_arm(args):
@@ -239,7 +240,7 @@ def run_reference_arm(args):
     per_step = max(1.0, min(8.0, 150.0 / max(1, args.steps + args.warmup)))
     times, flops, desc = [], 0.0, ""
     for i in range(args.warmup + args.steps):
-        f, dt, desc = cpu_oracle_sample(wl.mat_a, wl.mat_b, wl.sizes, per_step)
+        f, dt, desc = cpu_oracle_sample(wl.mat_a, wl.mat_b, wl.sizes, per_step, workload_rows=sum(sizes))
         if i >= args.warmup:
             times.append(dt)
             flops = f
@@ -293,6 +294,30 @@ def training_step_tflops(op, wl, steps: int, warmup: int):
     ms = time_steps(None, step, steps, warmup) / steps
     return {"value": 3.0 * wl.flops / (ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms, "steps": steps,
             "what": "forward + dA + dB per step, 3x the forward FLOPs"}
+
+
+def moe_routing_leg(dev, peaks, tokens: int = 16384, topk: int = 2, experts: int = 8, hidden: int = 4096):
+    """Times the caller-side steps around the GEMM at the Mixtral shape: expert ids -> offsets and
+    permutation, token-row gather, weighted scatter back. HBM-bound byte/index work."""
+    from grouped_mm_bf16_b200 import moe
+
+    gen = torch.Generator(device=dev).manual_seed(7)
+    ids = torch.randint(0, experts, (tokens, topk), device=dev, dtype=torch.int32, generator=gen)
+    x = torch.randn((tokens, hidden), device=dev, generator=gen).bfloat16()
+    w = torch.rand((tokens, topk), device=dev, generator=gen)
+    offs, perm, inv = moe.route(ids, experts)
+    y = moe.permute(x, perm, topk)
+    res = {}
+    legs = {
+        "route": (lambda: moe.route(ids, experts), tokens * topk * 4 * 3),              # ids read twice, perm+inv written
+        "permute": (lambda: moe.permute(x, perm, topk), (tokens + tokens * topk) * hidden * 2),
+        "combine": (lambda: moe.combine(y, inv, w, topk), (tokens * topk + tokens) * hidden * 2),
+    }
+    for name, (fn, nbytes) in legs.items():
+        ms = time_steps(None, fn, 50, 5) / 50
+        res[name] = {"us": ms * 1e3, "GB/s": nbytes / (ms * 1e-3) / 1e9, "frac_of_hbm_peak": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+    res["shape"] = f"{tokens} tokens, top-{topk}, {experts} experts, hidden {hidden}, bf16"
+    return res
 
 
 # ----------------------------------------------------------------------------- main arm
@@ -443,6 +468,10 @@ def main():
                     line["training_step"] = training_step_tflops(grouped_mm, wl, max(3, min(args.steps, 20)), 3)
                 except Exception as exc:  # informative legs must not hide the headline number
                     line["training_step_error"] = f"{type(exc).__name__}: {exc}"[:200]
+                try:
+                    line["moe_routing"] = moe_routing_leg(dev, peaks)
+                except Exception as exc:
+                    line["moe_routing_error"] = f"{type(exc).__name__}: {exc}"[:200]
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()

@@ -35,6 +35,10 @@ EXPORTED_SYMBOLS = (
     "grouped_mm_2d3d_static_scratch",
     "gmm_select_kernel",
     "gmm_check_status",
+    "gmm_route_workspace_bytes",
+    "gmm_route_build",
+    "gmm_permute_rows",
+    "gmm_combine_rows",
 )
 
 
@@ -97,6 +101,15 @@ def load() -> ctypes.CDLL:
         lib.gmm_select_kernel.argtypes = [ctypes.c_int32, tp, tp, tp, ctypes.c_uint32]
         lib.gmm_check_status.restype = ctypes.c_int
         lib.gmm_check_status.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32)]
+        vp, i32, i64 = ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64
+        lib.gmm_route_workspace_bytes.restype = ctypes.c_size_t
+        lib.gmm_route_workspace_bytes.argtypes = [i64, i32]
+        lib.gmm_route_build.restype = ctypes.c_int
+        lib.gmm_route_build.argtypes = [vp, i64, i32, vp, vp, vp, vp, ctypes.c_size_t, vp]
+        lib.gmm_permute_rows.restype = ctypes.c_int
+        lib.gmm_permute_rows.argtypes = [vp, i64, i64, i64, vp, i32, vp, i64, i64, vp]
+        lib.gmm_combine_rows.restype = ctypes.c_int
+        lib.gmm_combine_rows.argtypes = [vp, i32, i64, vp, vp, i32, i64, i32, vp, i32, i64, vp]
         _lib = lib
         return lib
 

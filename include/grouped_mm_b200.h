@@ -155,6 +155,40 @@ int gmm_select_kernel(int32_t form, const gmm_tensor_t* a, const gmm_tensor_t* b
  */
 int gmm_check_status(void* workspace, void* stream, int32_t* raw);
 
+/* ------------------------------------------------------------------------------------------
+ * Caller-side MoE steps around the 2D x 3D form: from per-token expert choices to the grouped row
+ * order and back. The reference does the first step on the host in its benchmark only
+ * (expert ids -> torch.bincount -> cumsum -> int32 offs, bench/bench_2d3d.py:131-138) and has no
+ * counterpart for the others. All of it runs on the device here, with no host synchronisation.
+ * "Assignment" i = (token i / topk, choice i % topk); ids outside [0, n_experts) are not routed.
+ */
+
+/* Bytes of device workspace gmm_route_build() needs (0 for invalid arguments). */
+size_t gmm_route_workspace_bytes(int64_t n_assignments, int32_t n_experts);
+
+/*
+ * Stable counting sort of the assignments by expert.
+ *   offs[e]     END offset of expert e's rows (int32, n_experts entries): grouped_mm's `offs`
+ *   perm[p]     assignment placed at sorted position p (-1 past the last routed assignment)
+ *   inv_perm[i] sorted position of assignment i, -1 if not routed (may be NULL)
+ * Inside an expert, rows keep the order of their assignment index.
+ */
+int gmm_route_build(const int32_t* expert_ids, int64_t n_assignments, int32_t n_experts, int32_t* offs,
+                    int32_t* perm, int32_t* inv_perm, void* workspace, size_t workspace_bytes, void* stream);
+
+/* dst row r = src row perm[r] / topk for r < n_out_rows; rows whose perm entry is -1 are left untouched. */
+int gmm_permute_rows(const void* src, int64_t src_rows, int64_t row_bytes, int64_t src_stride_bytes,
+                     const int32_t* perm, int32_t topk, void* dst, int64_t dst_stride_bytes, int64_t n_out_rows,
+                     void* stream);
+
+/*
+ * out[t, :] = sum over k < topk of weights[t * topk + k] * y[inv_perm[t * topk + k], :], accumulated
+ * in fp32 (weights NULL = all ones; unrouted choices are skipped). Strides in elements.
+ */
+int gmm_combine_rows(const void* y, int32_t y_dtype, int64_t y_stride, const int32_t* inv_perm, const float* weights,
+                     int32_t topk, int64_t n_tokens, int32_t n_cols, void* out, int32_t out_dtype, int64_t out_stride,
+                     void* stream);
+
 #ifdef __cplusplus
 }
 #endif
