@@ -270,6 +270,29 @@ def test_registered_torch_custom_op():
     assert torch.equal(got, want)
 
 
+@pytest.mark.parametrize("chunk_bytes", [1 << 12, 1 << 20, 1 << 30])
+def test_host_buffer_entry_matches_device_entry(chunk_bytes):
+    """grouped_mm_host (pinned host in/out, chunked copy/compute overlap) gives the bits of grouped_mm."""
+    from grouped_mm_bf16_b200.host import grouped_mm_host
+
+    sizes = [300, 0, 513, 255, 257, 0, 40, 0]
+    g = torch.Generator().manual_seed(41)
+    a = torch.randn((sum(sizes) + 11, 200), generator=g).bfloat16().pin_memory()  # 11 rows belong to no group
+    b = torch.randn((len(sizes), 200, 264), generator=g).bfloat16().pin_memory()
+    offs = torch.tensor(sizes, dtype=torch.int64).cumsum(0).to(torch.int32)
+    out = torch.full((a.size(0), 264), 7.0, dtype=torch.bfloat16).pin_memory()
+    for _ in range(2):  # the second call reuses the staging slots of the first
+        got = grouped_mm_host(a, b, offs, out=out, chunk_bytes=chunk_bytes)
+        torch.cuda.current_stream().synchronize()
+        want = grouped_mm(a.to(DEV), b.to(DEV), offs=offs.to(DEV)).cpu()
+        assert got is out and torch.equal(got[: sum(sizes)], want[: sum(sizes)])
+        assert bool((got[sum(sizes):] == 7.0).all()), "rows past offs[-1] were written"
+    ref, defined = grouped_mm_oracle(a, b, offs)
+    assert max_violation(out, ref, defined, atol_for(200, 1.0, 1.0)) <= 1.0
+    with pytest.raises(RuntimeError, match="host tensors"):
+        grouped_mm_host(a.to(DEV), b, offs)
+
+
 # ----------------------------------------------------------------------------- what must not be written
 
 
