@@ -293,6 +293,29 @@ def test_host_buffer_entry_matches_device_entry(chunk_bytes):
         grouped_mm_host(a.to(DEV), b, offs)
 
 
+def test_side_stream_and_cuda_graph_replay():
+    """The call only enqueues work on the current stream (no host sync, no allocation inside the
+    library), so it can run on a side stream and be captured into a CUDA graph and replayed."""
+    wl = make_workload("mixtral", DEV, seed=3, scale=1 / 32, dims_scale=1 / 8)
+    want = grouped_mm(wl.mat_a, wl.mat_b, offs=wl.offs)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        got = grouped_mm(wl.mat_a, wl.mat_b, offs=wl.offs)
+    side.synchronize()
+    assert torch.equal(got, want)
+
+    static_a = wl.mat_a.clone()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        static_out = grouped_mm(static_a, wl.mat_b, offs=wl.offs)
+    other = make_workload("mixtral", DEV, seed=4, scale=1 / 32, dims_scale=1 / 8, sizes=wl.sizes)
+    static_a.copy_(other.mat_a)
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(static_out, grouped_mm(other.mat_a, wl.mat_b, offs=wl.offs))
+
+
 # ----------------------------------------------------------------------------- what must not be written
 
 
