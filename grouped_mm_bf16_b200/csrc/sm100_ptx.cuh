@@ -80,7 +80,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 
 // Warp-level wait: lane 0 polls, the other lanes park at the shuffle instead of spinning
 // (fewer issue slots and less power spent by a warp that only has one thread of real work).
-// Returns the same verdict to every lane.
+// Returns the same answer to every lane.
 __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int lane) {
   int ok = 1;
   if (lane == 0) ok = mbar_wait(bar, parity, abort_flag) ? 1 : 0;
