@@ -35,6 +35,7 @@ EXPORTED_SYMBOLS = (
     "grouped_mm_2d3d_static_scratch",
     "gmm_select_kernel",
     "gmm_check_status",
+    "gmm_selftest_wait_timeout",
     "gmm_route_workspace_bytes",
     "gmm_route_build",
     "gmm_permute_rows",
@@ -102,6 +103,8 @@ def load() -> ctypes.CDLL:
         lib.gmm_check_status.restype = ctypes.c_int
         lib.gmm_check_status.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32)]
         vp, i32, i64 = ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64
+        lib.gmm_selftest_wait_timeout.restype = ctypes.c_int
+        lib.gmm_selftest_wait_timeout.argtypes = [vp, vp, i64]
         lib.gmm_route_workspace_bytes.restype = ctypes.c_size_t
         lib.gmm_route_workspace_bytes.argtypes = [i64, i32]
         lib.gmm_route_build.restype = ctypes.c_int

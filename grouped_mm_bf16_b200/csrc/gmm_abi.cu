@@ -453,6 +453,26 @@ int static_scratch(int dev, void** ptr) {
   return ss.status;
 }
 
+// ------------------------------------------------------------------ wait self-test
+//
+// One CTA waits, with a short budget, on an mbarrier that nothing will ever complete: the wait
+// gives up, the status word is set, the kernel returns normally and the context stays usable.
+// This is the path every bounded wait of the GEMM kernels takes if a producer or consumer goes
+// missing; it is exercised here without any real failure.
+__global__ void wait_selftest_kernel(int* status, long long budget_cycles) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    abort_flag = 0;
+    fence_barrier_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (!mbar_wait(&bar, 0, &abort_flag, 0, budget_cycles)) atomicCAS(status, 0, 0x7E57);
+  }
+}
+
 }  // namespace
 
 // ====================================================================== C ABI
@@ -539,6 +559,15 @@ int gmm_select_kernel(int32_t form, const gmm_tensor_t* a, const gmm_tensor_t* b
   const FastPlan plan = plan_fast(p, flags);
   if (!plan.ok) return GMM_KERNEL_GENERIC;
   return plan.pair ? GMM_KERNEL_TCGEN05_PAIR : GMM_KERNEL_TCGEN05;
+}
+
+int gmm_selftest_wait_timeout(void* workspace, void* stream, int64_t budget_cycles) {
+  if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 3u)) return GMM_ERR_WORKSPACE;
+  if (budget_cycles <= 0 || budget_cycles > kWaitBudgetCycles) return GMM_ERR_INVALID_ARGUMENT;
+  wait_selftest_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(reinterpret_cast<int*>(workspace),
+                                                                           (long long)budget_cycles);
+  GMM_CUDA_TRY(cudaGetLastError());
+  return GMM_OK;
 }
 
 int gmm_check_status(void* workspace, void* stream, int32_t* raw) {

@@ -64,13 +64,13 @@ constexpr long long kWaitBudgetCycles = 4000000000LL;
 // `backoff_ns` > 0 sleeps between polls: used where the wait is long (an epilogue warp waits
 // for a whole tile's main loop) so that idle warps do not compete for issue slots and power.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          unsigned backoff_ns = 0) {
+                                          unsigned backoff_ns = 0, long long budget_cycles = kWaitBudgetCycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (clock64() - t0 > kWaitBudgetCycles) {
+    if (clock64() - t0 > budget_cycles) {
       *abort_flag = 1;
       return false;
     }

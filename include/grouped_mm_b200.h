@@ -155,6 +155,15 @@ int gmm_select_kernel(int32_t form, const gmm_tensor_t* a, const gmm_tensor_t* b
  */
 int gmm_check_status(void* workspace, void* stream, int32_t* raw);
 
+/*
+ * Launches a one-CTA kernel that waits, for at most `budget_cycles` SM clocks (1 .. 4e9), on a
+ * barrier nothing completes. The wait gives up, writes code 0x7E57 to the status word of
+ * `workspace` and the kernel returns normally; gmm_check_status() then reports
+ * GMM_ERR_DEVICE_WAIT. It exercises, without any real failure, the give-up path that every
+ * bounded wait inside the GEMM kernels takes. No counterpart in the reference.
+ */
+int gmm_selftest_wait_timeout(void* workspace, void* stream, int64_t budget_cycles);
+
 /* ------------------------------------------------------------------------------------------
  * Caller-side MoE steps around the 2D x 3D form: from per-token expert choices to the grouped row
  * order and back. The reference does the first step on the host in its benchmark only

@@ -293,6 +293,19 @@ def test_host_buffer_entry_matches_device_entry(chunk_bytes):
         grouped_mm_host(a.to(DEV), b, offs)
 
 
+def test_torch_compile_traces_through_the_custom_op():
+    """Under torch.compile the call goes through the registered custom op (with its fake-tensor
+    rule); the "eager" backend runs dynamo's tracing without generating code, so this is quick."""
+    wl = make_workload("mixtral", DEV, seed=5, scale=1 / 64, dims_scale=1 / 8)
+
+    def fn(a, b, offs):
+        return grouped_mm(a, b, offs=offs).float() * 2.0
+
+    compiled = torch.compile(fn, backend="eager")
+    got = compiled(wl.mat_a, wl.mat_b, wl.offs)
+    assert torch.equal(got, fn(wl.mat_a, wl.mat_b, wl.offs))
+
+
 def test_side_stream_and_cuda_graph_replay():
     """The call only enqueues work on the current stream (no host sync, no allocation inside the
     library), so it can run on a side stream and be captured into a CUDA graph and replayed."""
@@ -500,3 +513,69 @@ def test_wgrad_full_size_groups_and_checksum():
     total = out[:, rows, :].sum(0).cpu()
     ref = wl.mat_a[rows].float().cpu() @ wl.mat_b.float().cpu()
     torch.testing.assert_close(total, ref, atol=atol_for(65536, 1, 1), rtol=8e-3)
+
+
+# ----------------------------------------------------------------------------- bounded waits
+
+
+def test_a_wait_that_runs_out_reports_a_status_and_leaves_the_gpu_usable(built_library):
+    """A wait on a barrier nothing completes gives up after its budget, the kernel returns, the
+    status word says so, and the next call works (no trap, no hang, context intact)."""
+    lib = _lib.load()
+    ws = torch.zeros(64, dtype=torch.int32, device=DEV)
+    stream = torch.cuda.current_stream().cuda_stream
+    assert lib.gmm_selftest_wait_timeout(ws.data_ptr(), stream, 2_000_000) == 0  # ~1 ms of waiting
+    raw = ctypes.c_int32(0)
+    rc = lib.gmm_check_status(ctypes.c_void_p(ws.data_ptr()), ctypes.c_void_p(stream), ctypes.byref(raw))
+    assert rc == _lib.GMM_ERR_DEVICE_WAIT and raw.value == 0x7E57
+    assert b"bounded wait" in lib.gmm_error_string(rc)
+    # the word was cleared by the check, and the device still computes
+    assert lib.gmm_check_status(ctypes.c_void_p(ws.data_ptr()), ctypes.c_void_p(stream), ctypes.byref(raw)) == 0
+    wl = make_workload("readme", DEV, seed=0)
+    _assert_parity(wl.mat_a, wl.mat_b, wl.offs, 1.0, 1.0)
+    assert lib.gmm_selftest_wait_timeout(ws.data_ptr(), stream, 0) == -1
+
+
+# ----------------------------------------------------------------------------- randomised shapes
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_random_shapes_layouts_and_dtypes(seed, tile_kernel):
+    """Random group patterns, aligned sizes, operand layouts, dtypes and output dtypes, all four forms."""
+    import random
+
+    rng = random.Random(seed)
+    g = torch.Generator(device=DEV).manual_seed(1000 + seed)
+    dtype = rng.choice([torch.bfloat16, torch.float16])
+    out_dtype = rng.choice([None, torch.float32])
+    n_groups = rng.randint(1, 12)
+    sizes = [rng.choice([0, 1, 8, 56, 127, 128, 129, 257, 400]) for _ in range(n_groups)]
+    dim = lambda: 8 * rng.randint(1, 70)  # noqa: E731  (multiples of 8: 16-byte aligned rows)
+
+    def mat(rows, cols, col_major, batch=None):
+        shape = (rows, cols) if batch is None else (batch, rows, cols)
+        if col_major:
+            shape = shape[:-2] + (cols, rows)
+            return torch.randn(shape, device=DEV, generator=g).to(dtype).transpose(-2, -1)
+        return torch.randn(shape, device=DEV, generator=g).to(dtype)
+
+    form = ["2d3d", "3d3d", "2d2d", "3d2d"][seed % 4]
+    if form == "2d3d":
+        k, n = dim(), dim()
+        a, b, offs = mat(sum(sizes) + rng.choice([0, 5]), k, False), mat(k, n, rng.random() < 0.5, n_groups), _offs(sizes)
+    elif form == "3d3d":
+        m, k, n = dim(), dim(), dim()
+        a, b, offs = mat(m, k, rng.random() < 0.5, n_groups), mat(k, n, rng.random() < 0.5, n_groups), None
+    elif form == "2d2d":
+        m, n = dim(), dim()
+        if sum(sizes) == 0:
+            sizes[0] = 8
+        a, b, offs = mat(m, sum(sizes), True), mat(sum(sizes), n, False), _offs(sizes)
+    else:
+        m, k = dim(), dim()
+        if sum(sizes) == 0:
+            sizes[0] = 8
+        a, b, offs = mat(m, k, rng.random() < 0.5, n_groups), mat(k, sum(sizes), True), _offs(sizes)
+    if a.numel() == 0:
+        pytest.skip("degenerate draw")
+    _assert_parity(a, b, offs, 1.0, 1.0, out_dtype, _lib.GMM_KERNEL_TCGEN05)
