@@ -54,10 +54,86 @@ def _flags() -> int:
     return _lib.GMM_FLAG_FORCE_GENERIC if os.environ.get("GROUPED_MM_B200_FORCE_GENERIC", "0") == "1" else 0
 
 
+# ---------------------------------------------------------------------------------------------
+# Re-laying out operands the TMA path cannot address.
+#
+# The tensor-core kernels need 16-bit operands whose rows start on 16-byte boundaries, and the
+# ragged dimension must not be the contiguous one. The reference accepts any row- or column-major
+# operand with any (odd) K and N, and so does this package: such calls run on the generic FMA
+# kernel, which is one to two orders of magnitude slower. For problems large enough to notice, the
+# operands are first copied into a layout the tensor-core kernels take (row pitch padded to a
+# multiple of 8 elements, ragged dimension made non-contiguous); the copy costs one pass over A and
+# B, the GEMM then runs at tensor-core speed. Values and results are unchanged.
+
+RELAYOUT_MIN_FLOPS = float(os.environ.get("GROUPED_MM_B200_RELAYOUT_MIN_FLOPS", 1 << 31))
+
+
+def _aligned_rows(t: torch.Tensor) -> bool:
+    """Row pitch, batch pitch and base address are multiples of 16 bytes for a 16-bit tensor."""
+    lead = t.stride(-2) if t.stride(-1) == 1 else t.stride(-1)
+    if t.data_ptr() % 16 or lead % 8:
+        return False
+    return t.dim() == 2 or t.size(0) <= 1 or (t.stride(0) % 8 == 0 and t.stride(0) > 0)
+
+
+def _relayout(t: torch.Tensor, row_major: bool) -> torch.Tensor:
+    """Same values and shape; last two dims row-major (or column-major) with a padded pitch."""
+    rows, cols = t.size(-2), t.size(-1)
+    batch = tuple(t.shape[:-2])
+    if row_major:
+        buf = torch.empty(batch + (rows, -(-cols // 8) * 8), dtype=t.dtype, device=t.device)
+        view = buf[..., :cols]
+    else:
+        buf = torch.empty(batch + (cols, -(-rows // 8) * 8), dtype=t.dtype, device=t.device)
+        view = buf[..., :rows].transpose(-2, -1)
+    view.copy_(t)
+    return view
+
+
+def _fix_operand(t: torch.Tensor, must_be_row_major: Optional[bool]) -> torch.Tensor:
+    is_row = t.stride(-1) == 1 and t.stride(-2) >= max(1, t.size(-1))
+    if must_be_row_major is None:
+        return t if _aligned_rows(t) else _relayout(t, is_row)
+    if is_row == must_be_row_major and _aligned_rows(t):
+        return t
+    return _relayout(t, must_be_row_major)
+
+
+def tensor_core_layouts(form: int, mat_a: torch.Tensor, mat_b: torch.Tensor):
+    """Returns (mat_a, mat_b), re-laid out where needed so that the tensor-core path applies.
+
+    Per form, the ragged dimension must not be contiguous: 2D x 3D needs a row-major A, 3D x 2D a
+    column-major B, 2D x 2D a column-major A and a row-major B; 3D x 3D takes either layout.
+    """
+    if form == _lib.FORM_2D3D:
+        return _fix_operand(mat_a, True), _fix_operand(mat_b, None)
+    if form == _lib.FORM_3D2D:
+        return _fix_operand(mat_a, None), _fix_operand(mat_b, False)
+    if form == _lib.FORM_2D2D:
+        return _fix_operand(mat_a, False), _fix_operand(mat_b, True)
+    return _fix_operand(mat_a, None), _fix_operand(mat_b, None)
+
+
+def _worth_relayout(form: int, mat_a: torch.Tensor, mat_b: torch.Tensor) -> bool:
+    if mat_a.dtype == torch.float32 or os.environ.get("GROUPED_MM_B200_FORCE_GENERIC", "0") == "1":
+        return False
+    if form == _lib.FORM_2D3D:
+        flops = 2.0 * mat_a.size(0) * mat_a.size(1) * mat_b.size(2)
+    elif form == _lib.FORM_3D3D:
+        flops = 2.0 * mat_a.size(0) * mat_a.size(1) * mat_a.size(2) * mat_b.size(2)
+    elif form == _lib.FORM_3D2D:
+        flops = 2.0 * mat_a.size(1) * mat_a.size(2) * mat_b.size(1)
+    else:
+        flops = 2.0 * mat_a.size(0) * mat_a.size(1) * mat_b.size(1)
+    return flops >= RELAYOUT_MIN_FLOPS
+
+
 def _launch(form: int, mat_a: torch.Tensor, mat_b: torch.Tensor, offs: Optional[torch.Tensor], out: torch.Tensor) -> None:
     lib = _lib.load()
     if not (mat_a.is_cuda and mat_b.is_cuda and out.is_cuda):
         raise RuntimeError("grouped_mm_b200 is GPU-only; CPU tensors are not supported")
+    if _worth_relayout(form, mat_a, mat_b):
+        mat_a, mat_b = tensor_core_layouts(form, mat_a, mat_b)
     dev = mat_a.device
     # The library launches on the current device: switch only when the tensors live elsewhere.
     switch = dev.index is not None and dev.index != torch.cuda.current_device()

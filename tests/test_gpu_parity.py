@@ -515,6 +515,44 @@ def test_wgrad_full_size_groups_and_checksum():
     torch.testing.assert_close(total, ref, atol=atol_for(65536, 1, 1), rtol=8e-3)
 
 
+# ----------------------------------------------------------------------------- large unaligned problems
+
+
+@pytest.mark.parametrize("form", ["2d3d", "2d3d_colmajor_a", "3d3d", "2d2d_rowmajor_a", "3d2d_rowmajor_b"])
+def test_large_unaligned_problems_are_relaid_out_for_the_tensor_cores(form):
+    """Odd K and N, or a contiguous ragged dimension, normally mean the generic kernel. Above a size
+    threshold the operands are copied into an aligned layout first, so the tensor-core kernels run;
+    the values, and so the result, are the same."""
+    g = torch.Generator(device=DEV).manual_seed(47)
+    sizes = [700, 0, 901]
+    rnd = lambda *shape: torch.randn(shape, device=DEV, generator=g).bfloat16()  # noqa: E731
+    if form == "2d3d":
+        a, b, offs, code = rnd(sum(sizes), 1001), rnd(3, 1001, 1003), _offs(sizes), _lib.FORM_2D3D
+    elif form == "2d3d_colmajor_a":
+        a, b, offs, code = rnd(1000, sum(sizes)).t(), rnd(3, 1000, 1003), _offs(sizes), _lib.FORM_2D3D
+    elif form == "3d3d":
+        a, b, offs, code = rnd(3, 701, 1001), rnd(3, 1001, 1003), None, _lib.FORM_3D3D
+    elif form == "2d2d_rowmajor_a":
+        a, b, offs, code = rnd(1001, sum(sizes)), rnd(sum(sizes), 1003), _offs(sizes), _lib.FORM_2D2D
+    else:
+        a, b, offs, code = rnd(3, 1001, 1000), rnd(1000, sum(sizes)), _offs(sizes), _lib.FORM_3D2D
+    out = grouped_mm(a, b, offs=offs)
+    assert _op.selected_kernel(code, a, b, out) == _lib.GMM_KERNEL_GENERIC  # as given: not addressable by TMA
+    assert _op._worth_relayout(code, a, b)
+    a2, b2 = _op.tensor_core_layouts(code, a, b)
+    assert torch.equal(a2, a) and torch.equal(b2, b)
+    assert _op.selected_kernel(code, a2, b2, out) in _lib.TCGEN05_KINDS
+    ref, defined = grouped_mm_oracle(a, b, offs)
+    if form == "2d2d_rowmajor_a":
+        for gi, (s0, e0) in enumerate(group_bounds(offs.cpu(), a.size(1))):
+            assert max_violation(out[gi], ref[gi], defined[gi], atol_for(e0 - s0, 1.0, 1.0)) <= 1.0
+    else:
+        assert max_violation(out, ref, defined, atol_for(a.size(-1), 1.0, 1.0)) <= 1.0
+    with force_generic():  # the generic kernel on the untouched operands agrees
+        slow = grouped_mm(a, b, offs=offs)
+    torch.testing.assert_close(out.float(), slow.float(), atol=2e-2 * 32, rtol=2e-2)
+
+
 # ----------------------------------------------------------------------------- bounded waits
 
 
