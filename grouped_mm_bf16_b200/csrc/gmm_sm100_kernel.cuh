@@ -316,7 +316,7 @@ gmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const int nkb = (klen + kBK - 1) / kBK;
       const int buf = it & 1;
       const uint32_t aph = (it >> 1) & 1;
-      if (!mbar_wait_warp(&tail.acc_empty[buf], aph ^ 1, abort_flag, lane)) {
+      if (!mbar_wait(&tail.acc_empty[buf], aph ^ 1, abort_flag)) {
         if (lane == 0) atomicCAS(p.status, 0, ST_MMA_TIMEOUT);
         ok = false;
         break;
@@ -324,7 +324,7 @@ gmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       tcgen05_fence_after_sync();
       const uint32_t d_tmem = tmem_base + buf * kBN;
       for (int kb = 0; kb < nkb; ++kb) {
-        if (!mbar_wait_warp(&tail.full[s], ph, abort_flag, lane)) {
+        if (!mbar_wait(&tail.full[s], ph, abort_flag)) {
           if (lane == 0) atomicCAS(p.status, 0, ST_MMA_TIMEOUT + 0x10);
           ok = false;
           break;

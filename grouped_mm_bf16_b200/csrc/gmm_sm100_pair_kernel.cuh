@@ -182,7 +182,7 @@ gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         const int nkb = (klen + kBK - 1) / kBK;
         const int buf = it & 1;
         const uint32_t aph = (it >> 1) & 1;
-        if (!mbar_wait_cluster_warp(&tail.acc_empty[buf], aph ^ 1, abort_flag, lane)) {
+        if (!mbar_wait_cluster(&tail.acc_empty[buf], aph ^ 1, abort_flag)) {
           if (lane == 0) atomicCAS(p.status, 0, ST_PAIR_MMA_TIMEOUT);
           ok = false;
           break;
@@ -190,7 +190,7 @@ gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         tcgen05_fence_after_sync();
         const uint32_t d_tmem = tmem_base + buf * kBN;
         for (int kb = 0; kb < nkb; ++kb) {
-          if (!mbar_wait_warp(&tail.full[s], ph, abort_flag, lane)) {
+          if (!mbar_wait(&tail.full[s], ph, abort_flag)) {
             if (lane == 0) atomicCAS(p.status, 0, ST_PAIR_MMA_TIMEOUT + 0x10);
             ok = false;
             break;
@@ -202,7 +202,7 @@ gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
               zero_tail_rows(smem_b + s * kPairBStageBytes, 2, r, lane);
             }
             __syncwarp();
-            if (!mbar_wait_cluster_warp(&tail.peer_ready[s], ph, abort_flag, lane)) {
+            if (!mbar_wait_cluster(&tail.peer_ready[s], ph, abort_flag)) {
               if (lane == 0) atomicCAS(p.status, 0, ST_PAIR_MMA_TIMEOUT + 0x20);
               ok = false;
               break;
@@ -237,7 +237,7 @@ gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         const int klen = tile_klen(p, tail.sched, t);
         const int nkb = (klen + kBK - 1) / kBK;
         for (int kb = 0; kb < nkb; ++kb) {
-          if (!mbar_wait_warp(&tail.full[s], ph, abort_flag, lane)) {
+          if (!mbar_wait(&tail.full[s], ph, abort_flag)) {
             if (lane == 0) atomicCAS(p.status, 0, ST_PAIR_RELAY_TIMEOUT);
             ok = false;
             break;

@@ -78,17 +78,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
-// Warp-level wait: lane 0 polls, the other lanes park at the shuffle instead of spinning
-// (fewer issue slots and less power spent by a warp that only has one thread of real work).
-// Returns the same answer to every lane.
-__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int lane) {
-  int ok = 1;
-  if (lane == 0) ok = mbar_wait(bar, parity, abort_flag) ? 1 : 0;
-  ok = __shfl_sync(0xffffffffu, ok, 0);
-  __syncwarp();  // orders the other lanes' later accesses after lane 0's acquire
-  return ok != 0;
-}
-
 // ---------------------------------------------------------------- fences
 
 // Makes generic-proxy writes to shared memory visible to the async proxy (TMA / tcgen05).
@@ -238,15 +227,6 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity
       return false;
     }
   }
-}
-
-__device__ __forceinline__ bool mbar_wait_cluster_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                                       int lane) {
-  int ok = 1;
-  if (lane == 0) ok = mbar_wait_cluster(bar, parity, abort_flag) ? 1 : 0;
-  ok = __shfl_sync(0xffffffffu, ok, 0);
-  __syncwarp();
-  return ok != 0;
 }
 
 // TMA load issued by either CTA of a pair; completion bytes are credited to the mbarrier at the
