@@ -18,6 +18,9 @@ GMM_BF16, GMM_F16, GMM_F32 = 0, 1, 2
 GMM_KERNEL_NONE, GMM_KERNEL_TCGEN05, GMM_KERNEL_GENERIC, GMM_KERNEL_TCGEN05_PAIR = 0, 1, 2, 3
 TCGEN05_KINDS = (GMM_KERNEL_TCGEN05, GMM_KERNEL_TCGEN05_PAIR)
 GMM_FLAG_FORCE_GENERIC = 0x1
+GMM_FLAG_FORCE_PAIR = 0x2
+GMM_FLAG_NO_PAIR = 0x4
+GMM_FLAG_ALLOW_TF32 = 0x8
 GMM_ERR_DEVICE_WAIT = -7
 
 FORM_3D3D, FORM_2D3D, FORM_3D2D, FORM_2D2D = 0, 1, 2, 3

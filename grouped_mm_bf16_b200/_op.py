@@ -50,41 +50,53 @@ def _desc(t: torch.Tensor) -> _lib.GmmTensor:
     return d
 
 
-def _flags() -> int:
-    return _lib.GMM_FLAG_FORCE_GENERIC if os.environ.get("GROUPED_MM_B200_FORCE_GENERIC", "0") == "1" else 0
+def _tf32_allowed() -> bool:
+    """fp32 operands may be multiplied as TF32 when torch's matmul knob says so, the setting the
+    reference passes to its kernels as ALLOW_TF32 (grouped_mm_bf16/kernels.py:185-194). The
+    reference reads the knob once per process; here it is read on every call."""
+    return bool(torch.backends.cuda.matmul.allow_tf32)
+
+
+def _flags(dtype: Optional[torch.dtype] = None) -> int:
+    flags = _lib.GMM_FLAG_FORCE_GENERIC if os.environ.get("GROUPED_MM_B200_FORCE_GENERIC", "0") == "1" else 0
+    if dtype == torch.float32 and _tf32_allowed():
+        flags |= _lib.GMM_FLAG_ALLOW_TF32
+    return flags
 
 
 # ---------------------------------------------------------------------------------------------
 # Re-laying out operands the TMA path cannot address.
 #
-# The tensor-core kernels need 16-bit operands whose rows start on 16-byte boundaries, and the
-# ragged dimension must not be the contiguous one. The reference accepts any row- or column-major
+# The tensor-core kernels need operands (16-bit, or fp32 when TF32 is allowed) whose rows start on
+# 16-byte boundaries, and the ragged dimension must not be the contiguous one. The reference accepts any row- or column-major
 # operand with any (odd) K and N, and so does this package: such calls run on the generic FMA
 # kernel, which is one to two orders of magnitude slower. For problems large enough to notice, the
 # operands are first copied into a layout the tensor-core kernels take (row pitch padded to a
-# multiple of 8 elements, ragged dimension made non-contiguous); the copy costs one pass over A and
+# multiple of 16 bytes, ragged dimension made non-contiguous); the copy costs one pass over A and
 # B, the GEMM then runs at tensor-core speed. Values and results are unchanged.
 
 RELAYOUT_MIN_FLOPS = float(os.environ.get("GROUPED_MM_B200_RELAYOUT_MIN_FLOPS", 1 << 31))
 
 
 def _aligned_rows(t: torch.Tensor) -> bool:
-    """Row pitch, batch pitch and base address are multiples of 16 bytes for a 16-bit tensor."""
+    """Row pitch, batch pitch and base address are multiples of 16 bytes."""
+    q = 16 // t.element_size()
     lead = t.stride(-2) if t.stride(-1) == 1 else t.stride(-1)
-    if t.data_ptr() % 16 or lead % 8:
+    if t.data_ptr() % 16 or lead % q:
         return False
-    return t.dim() == 2 or t.size(0) <= 1 or (t.stride(0) % 8 == 0 and t.stride(0) > 0)
+    return t.dim() == 2 or t.size(0) <= 1 or (t.stride(0) % q == 0 and t.stride(0) > 0)
 
 
 def _relayout(t: torch.Tensor, row_major: bool) -> torch.Tensor:
     """Same values and shape; last two dims row-major (or column-major) with a padded pitch."""
     rows, cols = t.size(-2), t.size(-1)
     batch = tuple(t.shape[:-2])
+    q = 16 // t.element_size()
     if row_major:
-        buf = torch.empty(batch + (rows, -(-cols // 8) * 8), dtype=t.dtype, device=t.device)
+        buf = torch.empty(batch + (rows, -(-cols // q) * q), dtype=t.dtype, device=t.device)
         view = buf[..., :cols]
     else:
-        buf = torch.empty(batch + (cols, -(-rows // 8) * 8), dtype=t.dtype, device=t.device)
+        buf = torch.empty(batch + (cols, -(-rows // q) * q), dtype=t.dtype, device=t.device)
         view = buf[..., :rows].transpose(-2, -1)
     view.copy_(t)
     return view
@@ -114,8 +126,10 @@ def tensor_core_layouts(form: int, mat_a: torch.Tensor, mat_b: torch.Tensor):
     return _fix_operand(mat_a, None), _fix_operand(mat_b, None)
 
 
-def _worth_relayout(form: int, mat_a: torch.Tensor, mat_b: torch.Tensor) -> bool:
-    if mat_a.dtype == torch.float32 or os.environ.get("GROUPED_MM_B200_FORCE_GENERIC", "0") == "1":
+def _worth_relayout(form: int, mat_a: torch.Tensor, mat_b: torch.Tensor, out: torch.Tensor) -> bool:
+    if os.environ.get("GROUPED_MM_B200_FORCE_GENERIC", "0") == "1":
+        return False
+    if mat_a.dtype == torch.float32 and not (_tf32_allowed() and out.dtype == torch.float32):
         return False
     if form == _lib.FORM_2D3D:
         flops = 2.0 * mat_a.size(0) * mat_a.size(1) * mat_b.size(2)
@@ -132,7 +146,7 @@ def _launch(form: int, mat_a: torch.Tensor, mat_b: torch.Tensor, offs: Optional[
     lib = _lib.load()
     if not (mat_a.is_cuda and mat_b.is_cuda and out.is_cuda):
         raise RuntimeError("grouped_mm_b200 is GPU-only; CPU tensors are not supported")
-    if _worth_relayout(form, mat_a, mat_b):
+    if _worth_relayout(form, mat_a, mat_b, out):
         mat_a, mat_b = tensor_core_layouts(form, mat_a, mat_b)
     dev = mat_a.device
     # The library launches on the current device: switch only when the tensors live elsewhere.
@@ -146,7 +160,7 @@ def _launch(form: int, mat_a: torch.Tensor, mat_b: torch.Tensor, offs: Optional[
         launch.stream = torch.cuda.current_stream(dev).cuda_stream
         launch.workspace = ws.data_ptr()
         launch.workspace_bytes = ws.numel() * 4
-        launch.flags = _flags()
+        launch.flags = _flags(mat_a.dtype)
         a, b, c = _desc(mat_a), _desc(mat_b), _desc(out)
         if form == _lib.FORM_3D3D:
             rc = lib.grouped_mm_3d3d(ctypes.byref(a), ctypes.byref(b), ctypes.byref(c), ctypes.byref(launch))
@@ -209,7 +223,7 @@ def selected_kernel(form: int, mat_a: torch.Tensor, mat_b: torch.Tensor, out: to
     3 tcgen05 CTA-pair)."""
     lib = _lib.load()
     a, b, c = _desc(mat_a), _desc(mat_b), _desc(out)
-    rc = lib.gmm_select_kernel(form, ctypes.byref(a), ctypes.byref(b), ctypes.byref(c), _flags())
+    rc = lib.gmm_select_kernel(form, ctypes.byref(a), ctypes.byref(b), ctypes.byref(c), _flags(mat_a.dtype))
     if rc < 0:
         raise RuntimeError(_lib.error_message(lib, rc))
     return rc

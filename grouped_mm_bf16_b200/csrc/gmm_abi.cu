@@ -80,6 +80,8 @@ int init_device(int dev) {
     if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_kernel<true, __nv_bfloat16>);
     if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_kernel<true, __half>);
     if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_kernel<true, float>);
+    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_kernel<false, float, 4>);
+    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_kernel<true, float, 4>);
     if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_pair_kernel<false, __nv_bfloat16>, kPairSmemBytes);
     if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_pair_kernel<false, __half>, kPairSmemBytes);
     if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_pair_kernel<false, float>, kPairSmemBytes);
@@ -207,27 +209,32 @@ int env_int(const char* name, int fallback) {
 
 bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; }
 
-// The TMA path needs 16-bit inputs, 16-byte aligned bases and leading/group strides, and the
-// ragged dimension must not be the contiguous one (a group may start at any index of it, while a
-// TMA box must start on a 16-byte boundary of the contiguous dimension).
+// The TMA path needs 16-byte aligned bases and leading/group strides, and the ragged dimension
+// must not be the contiguous one (a group may start at any index of it, while a TMA box must start
+// on a 16-byte boundary of the contiguous dimension). 16-bit inputs always qualify; fp32 inputs
+// only when the caller allows TF32 arithmetic (GMM_FLAG_ALLOW_TF32) and the output is fp32 -
+// otherwise fp32 stays on the generic kernel, which multiplies in true fp32.
 FastPlan plan_fast(const CanonProblem& p, uint32_t flags) {
   FastPlan f;
-  if (p.in_dtype == DT_F32 || p.K < 1) return f;
+  if (p.K < 1) return f;
+  const bool tf32 = (p.in_dtype == DT_F32);
+  if (tf32 && (!(flags & GMM_FLAG_ALLOW_TF32) || p.out_dtype != DT_F32)) return f;
+  const int q = tf32 ? 4 : 8;  // elements per 16 bytes
   if (!aligned16(p.a) || !aligned16(p.b)) return f;
-  if (p.a_sk == 1 && p.a_sm % 8 == 0 && p.a_sm >= p.K) f.a_mn = 0;
-  else if (p.a_sm == 1 && p.a_sk % 8 == 0 && p.a_sk >= p.M) f.a_mn = 1;
+  if (p.a_sk == 1 && p.a_sm % q == 0 && p.a_sm >= p.K) f.a_mn = 0;
+  else if (p.a_sm == 1 && p.a_sk % q == 0 && p.a_sk >= p.M) f.a_mn = 1;
   else return f;
-  if (p.b_sk == 1 && p.b_sn % 8 == 0 && p.b_sn >= p.K) f.b_mn = 0;
-  else if (p.b_sn == 1 && p.b_sk % 8 == 0 && p.b_sk >= p.N) f.b_mn = 1;
+  if (p.b_sk == 1 && p.b_sn % q == 0 && p.b_sn >= p.K) f.b_mn = 0;
+  else if (p.b_sn == 1 && p.b_sk % q == 0 && p.b_sk >= p.N) f.b_mn = 1;
   else return f;
-  if (p.mode == MODE_UNIFORM && p.G > 1 && (p.a_sg <= 0 || p.a_sg % 8 != 0)) return f;
-  if (p.mode != MODE_KRAGGED && p.G > 1 && (p.b_sg <= 0 || p.b_sg % 8 != 0)) return f;
+  if (p.mode == MODE_UNIFORM && p.G > 1 && (p.a_sg <= 0 || p.a_sg % q != 0)) return f;
+  if (p.mode != MODE_KRAGGED && p.G > 1 && (p.b_sg <= 0 || p.b_sg % q != 0)) return f;
   if (p.mode == MODE_MRAGGED && f.a_mn) return f;
   if (p.mode == MODE_KRAGGED && !(f.a_mn && f.b_mn)) return f;
   f.ok = true;
   // 256-row pair tiles pay off when groups are tall (little tail waste) and N spans both halves.
   // The group sizes live on the device, so the host decides on the mean rows per group.
-  if (p.N > kPairBNHalf) {
+  if (p.N > kPairBNHalf && !tf32) {
     const long long mean_rows = (p.mode == MODE_MRAGGED) ? (long long)p.M / (p.G > 0 ? p.G : 1) : p.M;
     f.pair = mean_rows >= 768;
     if (flags & GMM_FLAG_FORCE_PAIR) f.pair = true;
@@ -241,8 +248,10 @@ FastPlan plan_fast(const CanonProblem& p, uint32_t flags) {
 
 // ------------------------------------------------------------------ tensor maps
 
-// 3-D map (inner, outer, batch) over a 16-bit operand with a 128-byte-swizzled box.
-int encode_map(CUtensorMap* map, const void* base, int in_dtype, long long inner, long long outer,
+// 3-D map (inner, outer, batch) over an operand with a 128-byte-swizzled box: 64 16-bit or 32
+// 32-bit elements wide. `mn_major`: the inner dimension is M or N rather than K; a 32-bit operand
+// is then swizzled in 32-byte units, the layout tcgen05.mma reads such an operand in.
+int encode_map(CUtensorMap* map, const void* base, int in_dtype, bool mn_major, long long inner, long long outer,
                long long batch, long long outer_stride_elems, long long batch_stride_elems, int box_outer) {
   EncodeTiledFn enc = get_encode();
   if (!enc) {
@@ -251,12 +260,18 @@ int encode_map(CUtensorMap* map, const void* base, int in_dtype, long long inner
   }
   cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)outer, (cuuint64_t)(batch > 0 ? batch : 1)};
   if (batch <= 1) batch_stride_elems = outer_stride_elems * outer;
-  cuuint64_t strides[2] = {(cuuint64_t)outer_stride_elems * 2, (cuuint64_t)batch_stride_elems * 2};
-  cuuint32_t box[3] = {64, (cuuint32_t)box_outer, 1};
+  const unsigned es = (in_dtype == DT_F32) ? 4 : 2;
+  cuuint64_t strides[2] = {(cuuint64_t)outer_stride_elems * es, (cuuint64_t)batch_stride_elems * es};
+  cuuint32_t box[3] = {128 / es, (cuuint32_t)box_outer, 1};
   cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = enc(map, in_dtype == DT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+  const CUtensorMapDataType dt = in_dtype == DT_BF16  ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                 : in_dtype == DT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                      : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  const CUtensorMapSwizzle swz =
+      (es == 4 && mn_major) ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B;
+  CUresult r = enc(map, dt, 3,
                    const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     g_last_cuda_error = "cuTensorMapEncodeTiled failed with CUresult " + std::to_string((int)r);
@@ -266,7 +281,8 @@ int encode_map(CUtensorMap* map, const void* base, int in_dtype, long long inner
 }
 
 uint32_t make_idesc(int in_dtype, int a_mn, int b_mn, int mma_m) {
-  const uint32_t fmt = (in_dtype == DT_BF16) ? 1u : 0u;  // 0 = f16, 1 = bf16
+  // kind::f16: 0 = f16, 1 = bf16; kind::tf32: 2 = tf32
+  const uint32_t fmt = (in_dtype == DT_BF16) ? 1u : (in_dtype == DT_F32) ? 2u : 0u;
   uint32_t d = 0;
   d |= 1u << 4;                        // accumulator format: f32
   d |= fmt << 7;                       // A format
@@ -344,7 +360,7 @@ int launch_pair_t(const CUtensorMap& ta, const CUtensorMap& tb, const FastParams
 int choose_panel(const CanonProblem& p) {
   const int env = env_int("GROUPED_MM_B200_PANEL", 0);  // tuning knob
   if (env > 0) return env;
-  const long long tile_bytes = (long long)kBN * p.K * 2;
+  const long long tile_bytes = (long long)kBN * p.K * (p.in_dtype == DT_F32 ? 4 : 2);
   long long panel = (32ll << 20) / (tile_bytes > 0 ? tile_bytes : 1);
   if (panel < 2) panel = 2;
   if (panel > 64) panel = 64;
@@ -363,18 +379,20 @@ int launch_fast(const CanonProblem& p_in, const FastPlan& plan, const DeviceInfo
 
   const bool a_batched = (p.mode == MODE_UNIFORM);
   const bool b_batched = (p.mode != MODE_KRAGGED);
+  const bool tf32 = (p.in_dtype == DT_F32);
+  const int bk = tf32 ? ElemGeom<4>::BK : ElemGeom<2>::BK;  // k-rows per box of an MN-major operand
   CUtensorMap ta, tb;
   int rc;
   if (!plan.a_mn)
-    rc = encode_map(&ta, p.a, p.in_dtype, p.K, p.M, a_batched ? p.G : 1, p.a_sm, p.a_sg, 128);
+    rc = encode_map(&ta, p.a, p.in_dtype, false, p.K, p.M, a_batched ? p.G : 1, p.a_sm, p.a_sg, 128);
   else
-    rc = encode_map(&ta, p.a, p.in_dtype, p.M, p.K, a_batched ? p.G : 1, p.a_sk, p.a_sg, kBK);
+    rc = encode_map(&ta, p.a, p.in_dtype, true, p.M, p.K, a_batched ? p.G : 1, p.a_sk, p.a_sg, bk);
   if (rc != GMM_OK) return rc;
   if (!plan.b_mn)
-    rc = encode_map(&tb, p.b, p.in_dtype, p.K, p.N, b_batched ? p.G : 1, p.b_sn, p.b_sg,
+    rc = encode_map(&tb, p.b, p.in_dtype, false, p.K, p.N, b_batched ? p.G : 1, p.b_sn, p.b_sg,
                     plan.pair ? kPairBNHalf : kBN);
   else
-    rc = encode_map(&tb, p.b, p.in_dtype, p.N, p.K, b_batched ? p.G : 1, p.b_sk, p.b_sg, kBK);
+    rc = encode_map(&tb, p.b, p.in_dtype, true, p.N, p.K, b_batched ? p.G : 1, p.b_sk, p.b_sg, bk);
   if (rc != GMM_OK) return rc;
 
   FastParams fp;
@@ -388,6 +406,14 @@ int launch_fast(const CanonProblem& p_in, const FastPlan& plan, const DeviceInfo
       case DT_F16: return launch_pair_t<__half>(ta, tb, fp, grid, st);
       default: return launch_pair_t<float>(ta, tb, fp, grid, st);
     }
+  }
+  if (tf32) {
+    if (p.mode == MODE_KRAGGED)
+      gmm_sm100_kernel<true, float, 4><<<grid, kFastThreads, kFastSmemBytes, st>>>(ta, tb, fp);
+    else
+      gmm_sm100_kernel<false, float, 4><<<grid, kFastThreads, kFastSmemBytes, st>>>(ta, tb, fp);
+    GMM_CUDA_TRY(cudaGetLastError());
+    return GMM_OK;
   }
   return p.mode == MODE_KRAGGED ? launch_fast_kr<true>(ta, tb, fp, grid, st)
                                 : launch_fast_kr<false>(ta, tb, fp, grid, st);

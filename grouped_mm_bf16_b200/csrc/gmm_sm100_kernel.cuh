@@ -1,7 +1,8 @@
 // Persistent, warp-specialised grouped GEMM for sm_100a.
 //
 //   warp 0      TMA producer   : cp.async.bulk.tensor loads of A/B k-blocks into a 4-stage ring
-//   warp 1      MMA issuer     : tcgen05.mma (128 x 256 x 16, bf16/fp16 in, fp32 accumulate in TMEM)
+//   warp 1      MMA issuer     : tcgen05.mma (128 x 256 x 16, bf16/fp16 in, fp32 accumulate in TMEM;
+//                                or 128 x 256 x 8 with fp32 operands read as TF32)
 //   warps 2..5  epilogue       : tcgen05.ld -> one rounding to the output type -> masked global stores
 //
 // Each CTA owns 512 TMEM columns = two 128 x 256 fp32 accumulators, so the epilogue of tile i
@@ -33,6 +34,16 @@ constexpr int kBStageBytes = kBN * kBK * 2;          // 32 KiB
 constexpr int kStageBytes = kAStageBytes + kBStageBytes;
 constexpr int kChunkBytes = 64 * kBK * 2;            // one 64-wide MN chunk of an MN-major operand: 8 KiB
 constexpr int kTmemCols = 512;
+
+// Tile geometry by operand element size ES (2: bf16/fp16, 4: fp32 read as TF32). A stage always
+// holds 128-byte swizzle rows, so its size in bytes does not depend on ES; its extent along K does.
+template <int ES>
+struct ElemGeom {
+  static constexpr int BK = 128 / ES;           // elements of K per stage: 64 or 32
+  static constexpr int UMMA_K = 32 / ES;        // K per tcgen05.mma: 16 or 8
+  static constexpr int CHUNK_W = 128 / ES;      // MN elements per 128-byte row of an MN-major chunk
+  static constexpr int CHUNK_BYTES = BK * 128;  // one MN chunk: BK k-rows of 128 bytes (8 KiB or 4 KiB)
+};
 constexpr int kFastThreads = 192;
 constexpr int kEpilogueThreads = 128;
 constexpr unsigned kEpilogueBackoffNs = 128;  // sleep between polls while an epilogue warp waits for a tile
@@ -199,7 +210,7 @@ __device__ __forceinline__ void epilogue_store_warp(uint32_t t_row, TOut* c_warp
   }
 }
 
-template <bool KRAGGED, typename TOut>
+template <bool KRAGGED, typename TOut, int ES = 2>
 __global__ void __launch_bounds__(kFastThreads, 1)
 gmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const FastParams fp) {
@@ -212,6 +223,8 @@ gmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   uint8_t* epi_stage = smem + kStages * kStageBytes + ((sizeof(FastSmemTail) + 15) & ~size_t(15));
   volatile int* abort_flag = &tail.abort_flag;
 
+  using EG = ElemGeom<ES>;
+  constexpr int BK = EG::BK;
   const CanonProblem& p = fp.p;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -255,7 +268,7 @@ gmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const int t = tile_of_round<KRAGGED>(round, blockIdx.x, gridDim.x);
         if (t >= total) break;
         const TileInfo ti = decode_tile<kBM, kBN>(p, tail.sched, t);
-        const int nkb = (ti.klen + kBK - 1) / kBK;
+        const int nkb = (ti.klen + BK - 1) / BK;
         const int az = a_batched ? ti.g : 0;
         const int bz = b_batched ? ti.g : 0;
         for (int kb = 0; kb < nkb; ++kb) {
@@ -265,7 +278,7 @@ gmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             break;
           }
           mbar_arrive_expect_tx(&tail.full[s], kStageBytes);
-          const int k = ti.k0 + kb * kBK;
+          const int k = ti.k0 + kb * BK;
           uint8_t* sa = smem_a + s * kAStageBytes;
           uint8_t* sb = smem_b + s * kBStageBytes;
           auto load_a = [&](void* dst, int x, int y) { tma_load_3d(dst, &tmap_a, &tail.full[s], x, y, az); };
@@ -274,13 +287,15 @@ gmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             load_a(sa, k, ti.m0);
           } else {
 #pragma unroll
-            for (int c = 0; c < kBM / 64; ++c) load_a(sa + c * kChunkBytes, ti.m0 + c * 64, k);
+            for (int c = 0; c < kBM / EG::CHUNK_W; ++c)
+              load_a(sa + c * EG::CHUNK_BYTES, ti.m0 + c * EG::CHUNK_W, k);
           }
           if (!fp.b_mn) {
             load_b(sb, k, ti.n0);
           } else {
 #pragma unroll
-            for (int c = 0; c < kBN / 64; ++c) load_b(sb + c * kChunkBytes, ti.n0 + c * 64, k);
+            for (int c = 0; c < kBN / EG::CHUNK_W; ++c)
+              load_b(sb + c * EG::CHUNK_BYTES, ti.n0 + c * EG::CHUNK_W, k);
           }
           if (++s == kStages) { s = 0; ph ^= 1; }
         }
@@ -297,14 +312,20 @@ gmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (lane 0 issues)
-    // Descriptor geometry. K-major tile: rows of 128 B, 8-row swizzle atoms 1024 B apart; a
-    // 16-element k-step advances 32 B inside the swizzled row. MN-major tile: 64-wide MN
-    // chunks of [64 k-rows][128 B]; chunks are kChunkBytes apart (leading offset), 8-k-row atoms
-    // 1024 B apart (stride offset); a 16-row k-step advances 2048 B.
-    const uint32_t a_lbo = fp.a_mn ? kChunkBytes : 16;
-    const uint32_t b_lbo = fp.b_mn ? kChunkBytes : 16;
-    const uint32_t a_kstep = fp.a_mn ? (kUmmaK * 128) : (kUmmaK * 2);
-    const uint32_t b_kstep = fp.b_mn ? (kUmmaK * 128) : (kUmmaK * 2);
+    // Descriptor geometry. K-major tile: rows of 128 B, 8-row swizzle atoms 1024 B apart; one
+    // k-step (16 16-bit or 8 32-bit elements) advances 32 B inside the swizzled row. MN-major
+    // tile: chunks of [BK k-rows][128 B] covering 128 B of the MN dimension each; chunks are
+    // CHUNK_BYTES apart (leading offset), 8-k-row atoms 1024 B apart (stride offset); a k-step
+    // advances UMMA_K rows of 128 B. An MN-major 32-bit operand is swizzled in 32-byte units over
+    // 4-row atoms instead (the tensor map loads it that way), so its atoms are 512 B apart.
+    const uint32_t a_lbo = fp.a_mn ? EG::CHUNK_BYTES : 16;
+    const uint32_t b_lbo = fp.b_mn ? EG::CHUNK_BYTES : 16;
+    const uint32_t a_sbo = (ES == 4 && fp.a_mn) ? 512 : 1024;
+    const uint32_t b_sbo = (ES == 4 && fp.b_mn) ? 512 : 1024;
+    const uint32_t a_swz = (ES == 4 && fp.a_mn) ? kSwizzle128BBase32B : kSwizzle128B;
+    const uint32_t b_swz = (ES == 4 && fp.b_mn) ? kSwizzle128BBase32B : kSwizzle128B;
+    const uint32_t a_kstep = fp.a_mn ? (EG::UMMA_K * 128) : 32;
+    const uint32_t b_kstep = fp.b_mn ? (EG::UMMA_K * 128) : 32;
     int s = 0;
     uint32_t ph = 0;
     int it = 0;
@@ -313,7 +334,7 @@ gmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const int t = tile_of_round<KRAGGED>(it, blockIdx.x, gridDim.x);
       if (t >= total) break;
       const int klen = tile_klen(p, tail.sched, t);  // the issuer needs no tile coordinates
-      const int nkb = (klen + kBK - 1) / kBK;
+      const int nkb = (klen + BK - 1) / BK;
       const int buf = it & 1;
       const uint32_t aph = (it >> 1) & 1;
       if (!mbar_wait(&tail.acc_empty[buf], aph ^ 1, abort_flag)) {
@@ -334,20 +355,20 @@ gmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         uint8_t* sb = smem_b + s * kBStageBytes;
         if constexpr (KRAGGED) {
           // The last k-block of a group over-reads k-rows of the next group. Both operands are
-          // MN-major here, so k-rows are whole 128-byte lines: rows [r, 64) of every chunk form
+          // MN-major here, so k-rows are whole 128-byte lines: rows [r, BK) of every chunk form
           // one contiguous range, zeroed before the MMA so they contribute exactly 0.
-          const int r = klen - kb * kBK;
-          if (r < kBK) {
-            const int n16 = (kBK - r) * 8;  // 16-byte words per chunk
+          const int r = klen - kb * BK;
+          if (r < BK) {
+            const int n16 = (BK - r) * 8;  // 16-byte words per chunk
             const uint4 z = make_uint4(0, 0, 0, 0);
 #pragma unroll
-            for (int c = 0; c < kBM / 64; ++c) {
-              uint4* q = reinterpret_cast<uint4*>(sa + c * kChunkBytes + r * 128);
+            for (int c = 0; c < kBM / EG::CHUNK_W; ++c) {
+              uint4* q = reinterpret_cast<uint4*>(sa + c * EG::CHUNK_BYTES + r * 128);
               for (int i = lane; i < n16; i += 32) q[i] = z;
             }
 #pragma unroll
-            for (int c = 0; c < kBN / 64; ++c) {
-              uint4* q = reinterpret_cast<uint4*>(sb + c * kChunkBytes + r * 128);
+            for (int c = 0; c < kBN / EG::CHUNK_W; ++c) {
+              uint4* q = reinterpret_cast<uint4*>(sb + c * EG::CHUNK_BYTES + r * 128);
               for (int i = lane; i < n16; i += 32) q[i] = z;
             }
             fence_proxy_async_smem();
@@ -355,12 +376,16 @@ gmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           __syncwarp();
         }
         if (lane == 0) {
-          const uint64_t a_desc = make_smem_desc_sw128(smem_u32(sa), a_lbo, 1024);
-          const uint64_t b_desc = make_smem_desc_sw128(smem_u32(sb), b_lbo, 1024);
+          const uint64_t a_desc = make_smem_desc_sw128(smem_u32(sa), a_lbo, a_sbo, a_swz);
+          const uint64_t b_desc = make_smem_desc_sw128(smem_u32(sb), b_lbo, b_sbo, b_swz);
 #pragma unroll
-          for (int k = 0; k < kBK / kUmmaK; ++k) {
-            umma_f16_ss(d_tmem, a_desc + ((k * a_kstep) >> 4), b_desc + ((k * b_kstep) >> 4), fp.idesc,
-                        (kb | k) != 0 ? 1u : 0u);
+          for (int k = 0; k < BK / EG::UMMA_K; ++k) {
+            if constexpr (ES == 4)
+              umma_tf32_ss(d_tmem, a_desc + ((k * a_kstep) >> 4), b_desc + ((k * b_kstep) >> 4), fp.idesc,
+                           (kb | k) != 0 ? 1u : 0u);
+            else
+              umma_f16_ss(d_tmem, a_desc + ((k * a_kstep) >> 4), b_desc + ((k * b_kstep) >> 4), fp.idesc,
+                          (kb | k) != 0 ? 1u : 0u);
           }
           umma_commit(&tail.empty[s]);  // frees the stage once these MMAs have read it
         }

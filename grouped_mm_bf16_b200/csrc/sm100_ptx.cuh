@@ -132,15 +132,18 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
 
 // 64-bit shared-memory matrix descriptor (Blackwell format): start address, leading-dimension
 // and stride-dimension byte offsets (all >> 4), descriptor version 1 at bit 46, swizzle mode
-// at bits 61..63 (2 = 128-byte swizzle).
+// at bits 61..63: 2 = 128-byte swizzle of 16-byte units over 8 rows; 1 = 128-byte swizzle of
+// 32-byte units over 4 rows, the only swizzled layout an MN-major 32-bit operand may use.
+constexpr uint32_t kSwizzle128B = 2;
+constexpr uint32_t kSwizzle128BBase32B = 1;
 __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr, uint32_t lbo_bytes,
-                                                         uint32_t sbo_bytes) {
+                                                         uint32_t sbo_bytes, uint32_t swizzle = kSwizzle128B) {
   uint64_t d = 0;
   d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
   d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
   d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
   d |= 1ull << 46;
-  d |= 2ull << 61;
+  d |= static_cast<uint64_t>(swizzle) << 61;
   return d;
 }
 
@@ -152,6 +155,20 @@ __device__ __forceinline__ void umma_f16_ss(uint32_t d_tmem, uint64_t a_desc, ui
       ".reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}"
+      ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// Same with fp32 operands read as TF32 (the low 13 mantissa bits are ignored); K = 8 per instruction.
+__device__ __forceinline__ void umma_tf32_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t"
       "}"
       ::"r"(d_tmem),
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)

@@ -50,6 +50,11 @@ enum gmm_kernel_kind {
 #define GMM_FLAG_FORCE_GENERIC 0x1u /* route to the generic kernel even where the TMA path applies */
 #define GMM_FLAG_FORCE_PAIR 0x2u    /* tcgen05 path: always use the CTA-pair (cta_group::2) kernel if legal */
 #define GMM_FLAG_NO_PAIR 0x4u       /* tcgen05 path: never use the CTA-pair kernel */
+/* fp32 operands with an fp32 result may be multiplied as TF32 on the tensor cores (fp32 accumulate).
+ * Without it fp32 operands are multiplied in true fp32. Counterpart of the reference's ALLOW_TF32
+ * kernel argument, which it takes from torch.backends.cuda.matmul.allow_tf32
+ * (grouped_mm_bf16/kernels.py:185-194, 242). */
+#define GMM_FLAG_ALLOW_TF32 0x8u
 
 /*
  * A 2-D or 3-D strided tensor in device memory. Sizes and strides are in elements, outermost

@@ -79,6 +79,38 @@ def test_unaligned_or_fp32_shapes_take_the_generic_kernel(lib):
     assert _select(lib, _lib.FORM_2D3D, a, b, c) == _lib.GMM_KERNEL_GENERIC
 
 
+def test_fp32_takes_the_tcgen05_kernel_only_when_tf32_is_allowed(lib):
+    a = _tensor((32, 64), (64, 1), _lib.GMM_F32)
+    b = _tensor((6, 64, 48), (64 * 48, 48, 1), _lib.GMM_F32)
+    c = _tensor((32, 48), (48, 1), _lib.GMM_F32)
+    assert _select(lib, _lib.FORM_2D3D, a, b, c, _lib.GMM_FLAG_ALLOW_TF32) == _lib.GMM_KERNEL_TCGEN05
+    assert _select(lib, _lib.FORM_2D3D, a, b, c, 0) == _lib.GMM_KERNEL_GENERIC
+    both = _lib.GMM_FLAG_ALLOW_TF32 | _lib.GMM_FLAG_FORCE_GENERIC
+    assert _select(lib, _lib.FORM_2D3D, a, b, c, both) == _lib.GMM_KERNEL_GENERIC
+    # a 16-bit result of fp32 operands stays on the generic kernel
+    c16 = _tensor((32, 48), (48, 1), _lib.GMM_BF16)
+    assert _select(lib, _lib.FORM_2D3D, a, b, c16, _lib.GMM_FLAG_ALLOW_TF32) == _lib.GMM_KERNEL_GENERIC
+    # rows of fp32 must start on 16-byte boundaries: a pitch of 4 elements is enough, 6 is not
+    a4 = _tensor((32, 60), (60, 1), _lib.GMM_F32)
+    b4 = _tensor((6, 60, 44), (60 * 44, 44, 1), _lib.GMM_F32)
+    c4 = _tensor((32, 44), (44, 1), _lib.GMM_F32)
+    assert _select(lib, _lib.FORM_2D3D, a4, b4, c4, _lib.GMM_FLAG_ALLOW_TF32) == _lib.GMM_KERNEL_TCGEN05
+    a6 = _tensor((32, 62), (62, 1), _lib.GMM_F32)
+    b6 = _tensor((6, 62, 44), (62 * 44, 44, 1), _lib.GMM_F32)
+    assert _select(lib, _lib.FORM_2D3D, a6, b6, c4, _lib.GMM_FLAG_ALLOW_TF32) == _lib.GMM_KERNEL_GENERIC
+    # tall groups: 16-bit operands take the CTA-pair kernel, fp32 operands never do
+    at = _tensor((8192, 64), (64, 1), _lib.GMM_F32)
+    bt = _tensor((2, 64, 512), (64 * 512, 512, 1), _lib.GMM_F32)
+    ct = _tensor((8192, 512), (512, 1), _lib.GMM_F32)
+    flags = _lib.GMM_FLAG_ALLOW_TF32 | _lib.GMM_FLAG_FORCE_PAIR
+    assert _select(lib, _lib.FORM_2D3D, at, bt, ct, flags) == _lib.GMM_KERNEL_TCGEN05
+    # the flag changes nothing for 16-bit operands
+    a = _tensor((32, 64), (64, 1))
+    b = _tensor((6, 64, 48), (64 * 48, 48, 1))
+    c = _tensor((32, 48), (48, 1))
+    assert _select(lib, _lib.FORM_2D3D, a, b, c, _lib.GMM_FLAG_ALLOW_TF32) == _lib.GMM_KERNEL_TCGEN05
+
+
 def test_ragged_dimension_must_not_be_the_contiguous_one(lib):
     # 2D x 3D with column-major A: rows (ragged) are contiguous -> generic
     a = _tensor((32, 64), (1, 32))

@@ -232,6 +232,148 @@ def test_fp32_inputs_are_true_fp32():
     out = grouped_mm(a, b, offs=_offs(sizes))
     ref, _ = grouped_mm_oracle(a, b, _offs(sizes))
     torch.testing.assert_close(out.cpu(), ref, atol=3e-4, rtol=3e-4)
+    # aligned fp32 operands too, as long as torch's TF32 knob is off (its default)
+    assert not torch.backends.cuda.matmul.allow_tf32
+    a = torch.randn((32, 64), device=DEV, generator=g)
+    b = torch.randn((6, 64, 48), device=DEV, generator=g)
+    out = grouped_mm(a, b, offs=_offs(sizes))
+    assert _op.selected_kernel(_lib.FORM_2D3D, a, b, out) == _lib.GMM_KERNEL_GENERIC
+    ref, _ = grouped_mm_oracle(a, b, _offs(sizes))
+    torch.testing.assert_close(out.cpu(), ref, atol=3e-4, rtol=3e-4)
+
+
+# ----------------------------------------------------------------------------- fp32 operands as TF32
+
+
+class allow_tf32:
+    """Sets torch.backends.cuda.matmul.allow_tf32, the knob the reference hands to its kernels as
+    ALLOW_TF32 (kernels.py:185-194), for the duration of a block."""
+
+    def __enter__(self):
+        self.prev = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = True
+
+    def __exit__(self, *exc):
+        torch.backends.cuda.matmul.allow_tf32 = self.prev
+
+
+def _as_tf32(x):
+    """fp32 with the low 13 mantissa bits cleared: what the tensor cores read of an fp32 operand.
+    Keeps the shape and strides of ``x``."""
+    out = torch.empty_like(x)  # preserves the layout of dense, possibly transposed, tensors
+    out.copy_(x)
+    flat = out.as_strided((out.untyped_storage().nbytes() // 4,), (1,), 0)
+    flat.copy_((flat.view(torch.int32) & ~0x1FFF).view(torch.float32))
+    return out
+
+
+def _assert_tf32_parity(a, b, offs):
+    """With TF32 allowed the tcgen05 kernel runs; its result equals the fp32-accumulated product of
+    the TF32-truncated operands (to fp32 summation-order noise), and differs from the exact product
+    by at most 2^-9 sum|a||b| (two operands, each short of its fp32 value by less than 2^-10)."""
+    with allow_tf32():
+        out = grouped_mm(a, b, offs=offs)
+        assert out.dtype == torch.float32
+        assert _op.selected_kernel(FORMS[_form(a, b)], a, b, out) == _lib.GMM_KERNEL_TCGEN05
+    ref_t, defined = grouped_mm_oracle(_as_tf32(a), _as_tf32(b), offs)
+    torch.testing.assert_close(out.cpu()[defined], ref_t[defined], atol=1e-3, rtol=1e-4)
+    ref, _ = grouped_mm_oracle(a, b, offs)
+    bound, _ = grouped_mm_oracle(a.abs(), b.abs(), offs)
+    excess = ((out.cpu() - ref).abs() - (bound * 2.0 ** -9 + 1e-3))[defined]
+    assert excess.numel() == 0 or excess.max().item() <= 0.0
+    return out
+
+
+@pytest.mark.parametrize("a_col_major", [False, True])
+@pytest.mark.parametrize("b_col_major", [False, True])
+def test_tf32_3d3d_all_layouts(a_col_major, b_col_major):
+    g = torch.Generator(device=DEV).manual_seed(53)
+    G, m, k, n = 3, 136, 200, 264
+    a = torch.randn((G, k, m), device=DEV, generator=g).transpose(-2, -1) if a_col_major else \
+        torch.randn((G, m, k), device=DEV, generator=g)
+    b = torch.randn((G, n, k), device=DEV, generator=g).transpose(-2, -1) if b_col_major else \
+        torch.randn((G, k, n), device=DEV, generator=g)
+    _assert_tf32_parity(a, b, None)
+
+
+@pytest.mark.parametrize("sizes", M_PATTERNS)
+@pytest.mark.parametrize("k,n,b_col_major", [(64, 48, False), (200, 264, False), (72, 520, True), (4, 4, True)])
+def test_tf32_2d3d_tile_boundaries(sizes, k, n, b_col_major):
+    g = torch.Generator(device=DEV).manual_seed(len(sizes) * 1000 + k + n + 1)
+    a = torch.randn((sum(sizes), k), device=DEV, generator=g)
+    if b_col_major:
+        b = torch.randn((len(sizes), n, k), device=DEV, generator=g).transpose(-2, -1)
+    else:
+        b = torch.randn((len(sizes), k, n), device=DEV, generator=g)
+    out = _assert_tf32_parity(a, b, _offs(sizes))
+    if sum(sizes) == 0:
+        assert out.numel() == 0
+
+
+@pytest.mark.parametrize("sizes", K_PATTERNS)
+@pytest.mark.parametrize("m,n", [(16, 24), (136, 264), (128, 256)])
+def test_tf32_2d2d_k_ragged(sizes, m, n):
+    g = torch.Generator(device=DEV).manual_seed(sum(sizes) + m + 1)
+    kt = sum(sizes)
+    a = torch.randn((kt, m), device=DEV, generator=g).t()  # column-major [M, K_total]
+    b = torch.randn((kt, n), device=DEV, generator=g)
+    out = _assert_tf32_parity(a, b, _offs(sizes))
+    for gi, sz in enumerate(sizes):
+        if sz == 0:
+            assert not out[gi].any(), "an empty group has to give exact zeros"
+
+
+@pytest.mark.parametrize("sizes", [[7, 0, 1, 13, 11], [128, 130, 0, 60], [1, 0] * 10])
+def test_tf32_3d2d_n_ragged(sizes):
+    g = torch.Generator(device=DEV).manual_seed(59)
+    m, k, nt = 40, 48, sum(sizes)
+    a = torch.randn((len(sizes), m, k), device=DEV, generator=g)
+    b = torch.randn((nt, k), device=DEV, generator=g).t()
+    _assert_tf32_parity(a, b, _offs(sizes))
+
+
+def test_tf32_unaligned_operands_small_stay_generic_large_are_relaid_out():
+    g = torch.Generator(device=DEV).manual_seed(61)
+    sizes = [0, 7, 1, 13, 0, 11]
+    a = torch.randn((32, 29), device=DEV, generator=g)
+    b = torch.randn((6, 29, 31), device=DEV, generator=g)
+    with allow_tf32():
+        out = grouped_mm(a, b, offs=_offs(sizes))
+        assert _op.selected_kernel(_lib.FORM_2D3D, a, b, out) == _lib.GMM_KERNEL_GENERIC
+    ref, _ = grouped_mm_oracle(a, b, _offs(sizes))
+    torch.testing.assert_close(out.cpu(), ref, atol=3e-4, rtol=3e-4)  # true fp32 on the generic kernel
+    sizes = [700, 0, 901]
+    a = torch.randn((sum(sizes), 1001), device=DEV, generator=g)
+    b = torch.randn((3, 1001, 1003), device=DEV, generator=g)
+    with allow_tf32():
+        out = grouped_mm(a, b, offs=_offs(sizes))
+        assert _op._worth_relayout(_lib.FORM_2D3D, a, b, out)
+        a2, b2 = _op.tensor_core_layouts(_lib.FORM_2D3D, a, b)
+        assert torch.equal(a2, a) and torch.equal(b2, b)
+        assert _op.selected_kernel(_lib.FORM_2D3D, a2, b2, out) == _lib.GMM_KERNEL_TCGEN05
+    assert not _op._worth_relayout(_lib.FORM_2D3D, a, b, out)  # knob off again: fp32 stays true fp32
+    ref_t, _ = grouped_mm_oracle(_as_tf32(a), _as_tf32(b), _offs(sizes))
+    torch.testing.assert_close(out.cpu(), ref_t, atol=2e-3, rtol=1e-4)
+
+
+def test_tf32_backward_matches_fp32_reference():
+    """Gradients of fp32 operands run through the same kernels on transposed views."""
+    g = torch.Generator(device=DEV).manual_seed(67)
+    sizes = [129, 0, 255, 1, 40]
+    a = torch.randn((sum(sizes), 200), device=DEV, generator=g).requires_grad_()
+    b = torch.randn((len(sizes), 200, 264), device=DEV, generator=g).requires_grad_()
+    with allow_tf32():
+        out = grouped_mm(a, b, offs=_offs(sizes))
+        out.backward(torch.ones_like(out))
+    a_ref, b_ref = a.detach().clone().requires_grad_(), b.detach().clone().requires_grad_()
+    start = 0
+    pieces = []
+    for gi, sz in enumerate(sizes):
+        pieces.append(a_ref[start:start + sz] @ b_ref[gi])
+        start += sz
+    torch.cat(pieces).sum().backward()
+    torch.testing.assert_close(a.grad, a_ref.grad, atol=0.3, rtol=2e-2)
+    torch.testing.assert_close(b.grad, b_ref.grad, atol=0.3, rtol=2e-2)
 
 
 @pytest.mark.parametrize("form", ["2d3d", "3d2d", "2d2d"])
@@ -538,7 +680,7 @@ def test_large_unaligned_problems_are_relaid_out_for_the_tensor_cores(form):
         a, b, offs, code = rnd(3, 1001, 1000), rnd(1000, sum(sizes)), _offs(sizes), _lib.FORM_3D2D
     out = grouped_mm(a, b, offs=offs)
     assert _op.selected_kernel(code, a, b, out) == _lib.GMM_KERNEL_GENERIC  # as given: not addressable by TMA
-    assert _op._worth_relayout(code, a, b)
+    assert _op._worth_relayout(code, a, b, out)
     a2, b2 = _op.tensor_core_layouts(code, a, b)
     assert torch.equal(a2, a) and torch.equal(b2, b)
     assert _op.selected_kernel(code, a2, b2, out) in _lib.TCGEN05_KINDS
