@@ -320,6 +320,31 @@ def moe_routing_leg(dev, peaks, tokens: int = 16384, topk: int = 2, experts: int
     return res
 
 
+def gated_up_leg(dev, experts: int = 8, hidden: int = 4096, inter: int = 14336):
+    """Times the Mixtral-shape gated up-projection (weights [8, 4096, 2 x 14336]) with the activation
+    fused into the GEMM's epilogue, against grouped_mm followed by torch's silu and mul."""
+    from grouped_mm_bf16_b200 import grouped_mm, moe
+    from grouped_mm_bf16_b200.workloads import group_sizes
+
+    gen = torch.Generator(device=dev).manual_seed(11)
+    sizes = group_sizes("mixtral", 0)
+    x = torch.randn((sum(sizes), hidden), device=dev, generator=gen).bfloat16()
+    w = (torch.randn((experts, hidden, 2 * inter), device=dev, generator=gen) * 0.02).bfloat16()
+    offs = torch.tensor(sizes, dtype=torch.int64).cumsum(0).to(torch.int32).to(dev)
+    flops = 2.0 * sum(sizes) * hidden * 2 * inter
+
+    def two_step():
+        both = grouped_mm(x, w, offs=offs)
+        return torch.nn.functional.silu(both[:, :inter]) * both[:, inter:]
+
+    with torch.no_grad():
+        fused_ms = time_steps(None, lambda: moe.gated_up_projection(x, w, offs), 20, 3) / 20
+        two_ms = time_steps(None, two_step, 20, 3) / 20
+    return {"fused_ms": fused_ms, "fused_TFLOP/s": flops / (fused_ms * 1e-3) / 1e12, "two_step_ms": two_ms,
+            "shape": f"{sum(sizes)} rows, {experts} experts, {hidden} -> 2 x {inter}, bf16",
+            "what": "silu(x @ gate) * (x @ up): one kernel vs grouped_mm + torch silu * mul"}
+
+
 # ----------------------------------------------------------------------------- main arm
 
 
@@ -481,6 +506,10 @@ def main():
                     line["moe_routing"] = moe_routing_leg(dev, peaks)
                 except Exception as exc:
                     line["moe_routing_error"] = f"{type(exc).__name__}: {exc}"[:200]
+                try:
+                    line["gated_up_projection"] = gated_up_leg(dev)
+                except Exception as exc:
+                    line["gated_up_projection_error"] = f"{type(exc).__name__}: {exc}"[:200]
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()

@@ -22,6 +22,7 @@ GMM_FLAG_FORCE_PAIR = 0x2
 GMM_FLAG_NO_PAIR = 0x4
 GMM_FLAG_ALLOW_TF32 = 0x8
 GMM_ERR_DEVICE_WAIT = -7
+GMM_ERR_NOT_FUSABLE = -8
 
 FORM_3D3D, FORM_2D3D, FORM_3D2D, FORM_2D2D = 0, 1, 2, 3
 
@@ -35,6 +36,7 @@ EXPORTED_SYMBOLS = (
     "grouped_mm_2d2d",
     "grouped_mm_2d3d",
     "grouped_mm_3d2d",
+    "grouped_mm_2d3d_swiglu",
     "grouped_mm_2d3d_static_scratch",
     "gmm_select_kernel",
     "gmm_check_status",
@@ -94,7 +96,7 @@ def load() -> ctypes.CDLL:
         lib.gmm_workspace_bytes.argtypes = []
         lib.grouped_mm_3d3d.restype = ctypes.c_int
         lib.grouped_mm_3d3d.argtypes = [tp, tp, tp, lp]
-        for name in ("grouped_mm_2d2d", "grouped_mm_2d3d", "grouped_mm_3d2d"):
+        for name in ("grouped_mm_2d2d", "grouped_mm_2d3d", "grouped_mm_3d2d", "grouped_mm_2d3d_swiglu"):
             fn = getattr(lib, name)
             fn.restype = ctypes.c_int
             fn.argtypes = [tp, tp, ctypes.c_void_p, ctypes.c_int32, tp, lp]

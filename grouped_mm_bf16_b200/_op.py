@@ -218,6 +218,31 @@ def grouped_mm_3d2d(mat_a: torch.Tensor, mat_b: torch.Tensor, offs: torch.Tensor
     _dispatch(_lib.FORM_3D2D, mat_a, mat_b, offs, out)
 
 
+def grouped_mm_2d3d_swiglu(mat_a: torch.Tensor, gate_up: torch.Tensor, offs: torch.Tensor, out: torch.Tensor) -> bool:
+    """out[rows_g] = silu(mat_a[rows_g] @ gate_up[g][:, :N]) * (mat_a[rows_g] @ gate_up[g][:, N:]) in one
+    kernel. Returns False, having launched nothing, when the operands are not addressable by the
+    tensor-core path (the caller then multiplies and activates separately). No counterpart in the reference."""
+    lib = _lib.load()
+    if not (mat_a.is_cuda and gate_up.is_cuda and out.is_cuda):
+        raise RuntimeError("grouped_mm_b200 is GPU-only; CPU tensors are not supported")
+    dev = mat_a.device
+    with torch.cuda.device(dev):
+        ws = workspace(dev)
+        launch = _lib.GmmLaunch()
+        launch.stream = torch.cuda.current_stream(dev).cuda_stream
+        launch.workspace = ws.data_ptr()
+        launch.workspace_bytes = ws.numel() * 4
+        launch.flags = _flags(mat_a.dtype)
+        a, b, c = _desc(mat_a), _desc(gate_up), _desc(out)
+        rc = lib.grouped_mm_2d3d_swiglu(ctypes.byref(a), ctypes.byref(b), offs.data_ptr(), offs.numel(),
+                                        ctypes.byref(c), ctypes.byref(launch))
+    if rc == _lib.GMM_ERR_NOT_FUSABLE:
+        return False
+    if rc != 0:
+        raise RuntimeError(_lib.error_message(lib, rc))
+    return True
+
+
 def selected_kernel(form: int, mat_a: torch.Tensor, mat_b: torch.Tensor, out: torch.Tensor) -> int:
     """Which kernel a call with these tensors is routed to (0 none, 1 tcgen05 single-CTA, 2 generic,
     3 tcgen05 CTA-pair)."""

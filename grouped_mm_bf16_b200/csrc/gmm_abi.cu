@@ -82,6 +82,12 @@ int init_device(int dev) {
     if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_kernel<true, float>);
     if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_kernel<false, float, 4>);
     if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_kernel<true, float, 4>);
+    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_kernel<false, __nv_bfloat16, 2, true>);
+    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_kernel<false, __half, 2, true>);
+    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_kernel<false, float, 2, true>);
+    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_pair_kernel<false, __nv_bfloat16, true>, kPairSmemBytes);
+    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_pair_kernel<false, __half, true>, kPairSmemBytes);
+    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_pair_kernel<false, float, true>, kPairSmemBytes);
     if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_pair_kernel<false, __nv_bfloat16>, kPairSmemBytes);
     if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_pair_kernel<false, __half>, kPairSmemBytes);
     if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_pair_kernel<false, float>, kPairSmemBytes);
@@ -110,10 +116,13 @@ long long numel(const gmm_tensor_t* t) {
 }
 
 // form: 0 = 3d3d, 1 = 2d3d, 2 = 3d2d, 3 = 2d2d. On success *nothing is set when the call has no
-// work (empty output or no groups).
+// work (empty output or no groups). `swiglu` (form 1 only): b holds [gate | up], twice the output's
+// columns; the canonical N is the output's.
 int canonicalise(int form, const gmm_tensor_t* a, const gmm_tensor_t* b, const int32_t* offs, int n_groups,
-                 const gmm_tensor_t* out, CanonProblem* cp, bool* nothing, bool need_pointers) {
+                 const gmm_tensor_t* out, CanonProblem* cp, bool* nothing, bool need_pointers,
+                 bool swiglu = false) {
   *nothing = false;
+  if (swiglu && form != 1) return GMM_ERR_INVALID_ARGUMENT;
   const int a_nd = (form == 0 || form == 2) ? 3 : 2;
   const int b_nd = (form == 0 || form == 1) ? 3 : 2;
   const int c_nd = (form == 0 || form == 3) ? 3 : 2;
@@ -153,9 +162,10 @@ int canonicalise(int form, const gmm_tensor_t* a, const gmm_tensor_t* b, const i
     }
     case 1: {  // [Mt,K] x [G,K,N] -> [Mt,N]
       if (a->size[1] != b->size[1] || b->size[0] != n_groups) return GMM_ERR_INVALID_ARGUMENT;
-      if (out->size[0] != a->size[0] || out->size[1] != b->size[2]) return GMM_ERR_INVALID_ARGUMENT;
+      if (out->size[0] != a->size[0] || out->size[1] * (swiglu ? 2 : 1) != b->size[2])
+        return GMM_ERR_INVALID_ARGUMENT;
       p.mode = MODE_MRAGGED;
-      p.G = n_groups; p.M = (int)a->size[0]; p.K = (int)a->size[1]; p.N = (int)b->size[2];
+      p.G = n_groups; p.M = (int)a->size[0]; p.K = (int)a->size[1]; p.N = (int)out->size[1];
       p.a_sg = 0; p.a_sm = a->stride[0]; p.a_sk = a->stride[1];
       p.b_sg = b->stride[0]; p.b_sk = b->stride[1]; p.b_sn = b->stride[2];
       p.c_sg = 0; p.c_sm = out->stride[0]; p.c_sn = out->stride[1];
@@ -214,10 +224,11 @@ bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u
 // on a 16-byte boundary of the contiguous dimension). 16-bit inputs always qualify; fp32 inputs
 // only when the caller allows TF32 arithmetic (GMM_FLAG_ALLOW_TF32) and the output is fp32 -
 // otherwise fp32 stays on the generic kernel, which multiplies in true fp32.
-FastPlan plan_fast(const CanonProblem& p, uint32_t flags) {
+FastPlan plan_fast(const CanonProblem& p, uint32_t flags, bool swiglu = false) {
   FastPlan f;
   if (p.K < 1) return f;
   const bool tf32 = (p.in_dtype == DT_F32);
+  if (swiglu && tf32) return f;
   if (tf32 && (!(flags & GMM_FLAG_ALLOW_TF32) || p.out_dtype != DT_F32)) return f;
   const int q = tf32 ? 4 : 8;  // elements per 16 bytes
   if (!aligned16(p.a) || !aligned16(p.b)) return f;
@@ -231,10 +242,12 @@ FastPlan plan_fast(const CanonProblem& p, uint32_t flags) {
   if (p.mode != MODE_KRAGGED && p.G > 1 && (p.b_sg <= 0 || p.b_sg % q != 0)) return f;
   if (p.mode == MODE_MRAGGED && f.a_mn) return f;
   if (p.mode == MODE_KRAGGED && !(f.a_mn && f.b_mn)) return f;
+  // The up half of a row-major B starts at column N: a TMA box may only start there if N is a multiple of 16 bytes.
+  if (swiglu && f.b_mn && (p.N % q != 0 || p.b_sk < 2ll * p.N)) return f;
   f.ok = true;
   // 256-row pair tiles pay off when groups are tall (little tail waste) and N spans both halves.
   // The group sizes live on the device, so the host decides on the mean rows per group.
-  if (p.N > kPairBNHalf && !tf32) {
+  if ((p.N > kPairBNHalf || swiglu) && !tf32) {
     const long long mean_rows = (p.mode == MODE_MRAGGED) ? (long long)p.M / (p.G > 0 ? p.G : 1) : p.M;
     f.pair = mean_rows >= 768;
     if (flags & GMM_FLAG_FORCE_PAIR) f.pair = true;
@@ -367,11 +380,23 @@ int choose_panel(const CanonProblem& p) {
   return (int)panel;
 }
 
-int launch_fast(const CanonProblem& p_in, const FastPlan& plan, const DeviceInfo& d, cudaStream_t st) {
+template <typename TOut>
+int launch_swiglu_t(const CUtensorMap& ta, const CUtensorMap& tb, const FastParams& fp, bool pair, int grid,
+                    cudaStream_t st) {
+  if (pair)
+    gmm_sm100_pair_kernel<false, TOut, true><<<grid, kFastThreads, kPairSmemBytes, st>>>(ta, tb, fp);
+  else
+    gmm_sm100_kernel<false, TOut, 2, true><<<grid, kFastThreads, kFastSmemBytes, st>>>(ta, tb, fp);
+  GMM_CUDA_TRY(cudaGetLastError());
+  return GMM_OK;
+}
+
+int launch_fast(const CanonProblem& p_in, const FastPlan& plan, const DeviceInfo& d, cudaStream_t st,
+                bool swiglu = false) {
   CanonProblem p = p_in;
   const int bm = plan.pair ? kPairBM : kBM;
   p.panel = choose_panel(p);
-  const long long ub = tile_upper_bound(p, bm, kBN);
+  const long long ub = tile_upper_bound(p, bm, swiglu ? kBN / 2 : kBN);
   if (ub <= 0) return GMM_OK;
   if (ub > 0x7fffffffLL) return GMM_ERR_INVALID_ARGUMENT;
   const int units = plan.pair ? d.sm_count / 2 : d.sm_count;
@@ -388,11 +413,12 @@ int launch_fast(const CanonProblem& p_in, const FastPlan& plan, const DeviceInfo
   else
     rc = encode_map(&ta, p.a, p.in_dtype, true, p.M, p.K, a_batched ? p.G : 1, p.a_sk, p.a_sg, bk);
   if (rc != GMM_OK) return rc;
+  const long long b_cols = swiglu ? 2ll * p.N : p.N;  // [gate | up] when the activation is fused
   if (!plan.b_mn)
-    rc = encode_map(&tb, p.b, p.in_dtype, false, p.K, p.N, b_batched ? p.G : 1, p.b_sn, p.b_sg,
-                    plan.pair ? kPairBNHalf : kBN);
+    rc = encode_map(&tb, p.b, p.in_dtype, false, p.K, b_cols, b_batched ? p.G : 1, p.b_sn, p.b_sg,
+                    (plan.pair || swiglu) ? kPairBNHalf : kBN);
   else
-    rc = encode_map(&tb, p.b, p.in_dtype, true, p.N, p.K, b_batched ? p.G : 1, p.b_sk, p.b_sg, bk);
+    rc = encode_map(&tb, p.b, p.in_dtype, true, b_cols, p.K, b_batched ? p.G : 1, p.b_sk, p.b_sg, bk);
   if (rc != GMM_OK) return rc;
 
   FastParams fp;
@@ -400,6 +426,13 @@ int launch_fast(const CanonProblem& p_in, const FastPlan& plan, const DeviceInfo
   fp.a_mn = plan.a_mn;
   fp.b_mn = plan.b_mn;
   fp.idesc = make_idesc(p.in_dtype, plan.a_mn, plan.b_mn, plan.pair ? 256 : 128);
+  if (swiglu) {
+    switch (p.out_dtype) {
+      case DT_BF16: return launch_swiglu_t<__nv_bfloat16>(ta, tb, fp, plan.pair, grid, st);
+      case DT_F16: return launch_swiglu_t<__half>(ta, tb, fp, plan.pair, grid, st);
+      default: return launch_swiglu_t<float>(ta, tb, fp, plan.pair, grid, st);
+    }
+  }
   if (plan.pair) {
     switch (p.out_dtype) {
       case DT_BF16: return launch_pair_t<__nv_bfloat16>(ta, tb, fp, grid, st);
@@ -422,11 +455,11 @@ int launch_fast(const CanonProblem& p_in, const FastPlan& plan, const DeviceInfo
 constexpr size_t kWorkspaceBytes = 256;
 
 int run(int form, const gmm_tensor_t* a, const gmm_tensor_t* b, const int32_t* offs, int n_groups,
-        const gmm_tensor_t* out, const gmm_launch_t* launch) {
+        const gmm_tensor_t* out, const gmm_launch_t* launch, bool swiglu = false) {
   if (!launch) return GMM_ERR_INVALID_ARGUMENT;
   CanonProblem p;
   bool nothing;
-  int rc = canonicalise(form, a, b, offs, n_groups, out, &p, &nothing, true);
+  int rc = canonicalise(form, a, b, offs, n_groups, out, &p, &nothing, true, swiglu);
   if (rc != GMM_OK) return rc;
   if (nothing) return GMM_OK;
   if (!launch->workspace || launch->workspace_bytes < kWorkspaceBytes ||
@@ -442,7 +475,9 @@ int run(int form, const gmm_tensor_t* a, const gmm_tensor_t* b, const int32_t* o
   const DeviceInfo& d = g_dev[dev];
   cudaStream_t st = reinterpret_cast<cudaStream_t>(launch->stream);
 
-  const FastPlan plan = (launch->flags & GMM_FLAG_FORCE_GENERIC) ? FastPlan() : plan_fast(p, launch->flags);
+  const FastPlan plan =
+      (launch->flags & GMM_FLAG_FORCE_GENERIC) ? FastPlan() : plan_fast(p, launch->flags, swiglu);
+  if (swiglu) return plan.ok ? launch_fast(p, plan, d, st, true) : GMM_ERR_NOT_FUSABLE;
   return plan.ok ? launch_fast(p, plan, d, st) : launch_generic(p, d, st);
 }
 
@@ -517,6 +552,8 @@ const char* gmm_error_string(int status) {
     case GMM_ERR_CUDA: return "CUDA call failed";
     case GMM_ERR_NOT_SM100: return "device is not compute capability 10.x (B200)";
     case GMM_ERR_DEVICE_WAIT: return "a bounded wait inside the kernel gave up; outputs are invalid";
+    case GMM_ERR_NOT_FUSABLE:
+      return "operands not addressable by the tensor-core path; run grouped_mm_2d3d and apply the activation separately";
     default: return "unknown status";
   }
 }
@@ -538,6 +575,11 @@ int grouped_mm_2d3d(const gmm_tensor_t* a, const gmm_tensor_t* b, const int32_t*
 int grouped_mm_3d2d(const gmm_tensor_t* a, const gmm_tensor_t* b, const int32_t* offs, int32_t n_groups,
                     const gmm_tensor_t* out, const gmm_launch_t* launch) {
   return run(2, a, b, offs, n_groups, out, launch);
+}
+
+int grouped_mm_2d3d_swiglu(const gmm_tensor_t* a, const gmm_tensor_t* b_gate_up, const int32_t* offs,
+                           int32_t n_groups, const gmm_tensor_t* out, const gmm_launch_t* launch) {
+  return run(1, a, b_gate_up, offs, n_groups, out, launch, true);
 }
 
 int grouped_mm_2d2d(const gmm_tensor_t* a, const gmm_tensor_t* b, const int32_t* offs, int32_t n_groups,

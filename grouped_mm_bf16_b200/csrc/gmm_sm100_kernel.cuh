@@ -210,7 +210,74 @@ __device__ __forceinline__ void epilogue_store_warp(uint32_t t_row, TOut* c_warp
   }
 }
 
-template <bool KRAGGED, typename TOut, int ES = 2>
+// The same for a tile whose accumulator holds two 128-column halves, G (columns 0..127) and U
+// (128..255): the stored tile has 128 columns, silu(G) * U evaluated on the fp32 accumulators.
+// Works through 32 columns at a time (one tcgen05.ld of each half) to keep the register count down.
+__device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
+
+template <typename TOut>
+__device__ __forceinline__ void epilogue_store_warp_swiglu(uint32_t t_row, TOut* c_warp, long long c_sm,
+                                                           long long c_sn, int rows, int ncols, uint8_t* stage,
+                                                           int lane) {
+  constexpr int CW = 128 / (int)sizeof(TOut);
+  const bool rows_aligned = (c_sn == 1) && ((reinterpret_cast<uintptr_t>(c_warp) & 15u) == 0) &&
+                            (((c_sm * (long long)sizeof(TOut)) & 15) == 0);
+  const bool row_ok = lane < rows;
+  TOut* c_row = c_warp + (long long)lane * c_sm;
+#pragma unroll 1
+  for (int c0 = 0; c0 < ncols; c0 += CW) {
+    const bool whole = rows_aligned && c0 + CW <= ncols;
+#pragma unroll 1
+    for (int h = 0; h < CW / 32; ++h) {
+      const int c = c0 + 32 * h;
+      if (c >= ncols) break;
+      uint32_t v[32], up[32];
+      tmem_ld_32x32b_x32(t_row + c, v);
+      tmem_ld_32x32b_x32(t_row + 128 + c, up);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(silu_mul(__uint_as_float(v[i]), __uint_as_float(up[i])));
+      if (whole) {
+        uint4* mine = reinterpret_cast<uint4*>(stage + lane * kStageRowBytes + h * 32 * (int)sizeof(TOut));
+        if constexpr (sizeof(TOut) == 4) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) mine[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 w;
+            w.x = OutCvt<TOut>::pack2(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]));
+            w.y = OutCvt<TOut>::pack2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
+            w.z = OutCvt<TOut>::pack2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
+            w.w = OutCvt<TOut>::pack2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
+            mine[j] = w;
+          }
+        }
+      } else if (row_ok) {
+        store_row_chunk<TOut>(c_row + (long long)c * c_sn, c_sn, v, min(32, ncols - c));
+      }
+    }
+    if (whole) {
+      __syncwarp();
+      const int seg = lane & 7;
+      const int sub = lane >> 3;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int row = i * 4 + sub;
+        const uint4 w = *reinterpret_cast<const uint4*>(stage + row * kStageRowBytes + seg * 16);
+        if (row < rows) {
+          uint8_t* dst = reinterpret_cast<uint8_t*>(c_warp + (long long)row * c_sm + c0) + seg * 16;
+          *reinterpret_cast<uint4*>(dst) = w;
+        }
+      }
+      __syncwarp();
+    }
+  }
+}
+
+// SWIGLU (row-ragged mode, 16-bit operands): B holds 2 N columns per group, [gate | up]; an output
+// tile has 128 columns, its accumulator the matching 128 gate and 128 up columns side by side.
+template <bool KRAGGED, typename TOut, int ES = 2, bool SWIGLU = false>
 __global__ void __launch_bounds__(kFastThreads, 1)
 gmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const FastParams fp) {
@@ -225,6 +292,8 @@ gmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
   using EG = ElemGeom<ES>;
   constexpr int BK = EG::BK;
+  constexpr int BNT = SWIGLU ? kBN / 2 : kBN;  // output columns per tile
+  static_assert(!SWIGLU || (!KRAGGED && ES == 2), "the fused activation exists for 16-bit row-ragged problems");
   const CanonProblem& p = fp.p;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -248,7 +317,7 @@ gmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     tmem_alloc(&tail.tmem_base, kTmemCols);
     tmem_relinquish();
   }
-  sched_init<kBM, kBN>(p, tail.sched);  // ends with __syncthreads()
+  sched_init<kBM, BNT>(p, tail.sched);  // ends with __syncthreads()
   tcgen05_fence_before_sync();
   __syncthreads();
   tcgen05_fence_after_sync();
@@ -267,7 +336,7 @@ gmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       for (int round = 0; ok; ++round) {
         const int t = tile_of_round<KRAGGED>(round, blockIdx.x, gridDim.x);
         if (t >= total) break;
-        const TileInfo ti = decode_tile<kBM, kBN>(p, tail.sched, t);
+        const TileInfo ti = decode_tile<kBM, BNT>(p, tail.sched, t);
         const int nkb = (ti.klen + BK - 1) / BK;
         const int az = a_batched ? ti.g : 0;
         const int bz = b_batched ? ti.g : 0;
@@ -290,7 +359,17 @@ gmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             for (int c = 0; c < kBM / EG::CHUNK_W; ++c)
               load_a(sa + c * EG::CHUNK_BYTES, ti.m0 + c * EG::CHUNK_W, k);
           }
-          if (!fp.b_mn) {
+          if constexpr (SWIGLU) {
+            // gate columns [n0, n0 + 128) and up columns [N + n0, N + n0 + 128) of B
+            if (!fp.b_mn) {
+              load_b(sb, k, ti.n0);  // boxes of 128 rows here
+              load_b(sb + kBStageBytes / 2, k, p.N + ti.n0);
+            } else {
+#pragma unroll
+              for (int c = 0; c < 4; ++c)
+                load_b(sb + c * EG::CHUNK_BYTES, (c < 2 ? 0 : p.N - 128) + ti.n0 + c * 64, k);
+            }
+          } else if (!fp.b_mn) {
             load_b(sb, k, ti.n0);
           } else {
 #pragma unroll
@@ -404,7 +483,7 @@ gmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     for (; ok; ++it) {
       const int t = tile_of_round<KRAGGED>(it, blockIdx.x, gridDim.x);
       if (t >= total) break;
-      const TileInfo ti = decode_tile<kBM, kBN>(p, tail.sched, t);
+      const TileInfo ti = decode_tile<kBM, BNT>(p, tail.sched, t);
       const int buf = it & 1;
       const uint32_t aph = (it >> 1) & 1;
       if (!mbar_wait(&tail.acc_full[buf], aph, abort_flag, kEpilogueBackoffNs)) {
@@ -417,9 +496,13 @@ gmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       TOut* c_warp = c_base + (long long)ti.g * p.c_sg + (long long)(ti.m0 + q * 32) * p.c_sm +
                      (long long)ti.n0 * p.c_sn;
       const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + buf * kBN;
-      const int ncols_tile = min(kBN, p.N - ti.n0);
-      epilogue_store_warp<TOut>(t_row, c_warp, p.c_sm, p.c_sn, ti.rows - q * 32, ncols_tile,
-                                epi_stage + (warp - 2) * kWarpStageBytes, zero_tile, lane);
+      const int ncols_tile = min(BNT, p.N - ti.n0);
+      if constexpr (SWIGLU)
+        epilogue_store_warp_swiglu<TOut>(t_row, c_warp, p.c_sm, p.c_sn, ti.rows - q * 32, ncols_tile,
+                                         epi_stage + (warp - 2) * kWarpStageBytes, lane);
+      else
+        epilogue_store_warp<TOut>(t_row, c_warp, p.c_sm, p.c_sn, ti.rows - q * 32, ncols_tile,
+                                  epi_stage + (warp - 2) * kWarpStageBytes, zero_tile, lane);
       tcgen05_fence_before_sync();
       mbar_arrive(&tail.acc_empty[buf]);
     }

@@ -66,7 +66,10 @@ __device__ __forceinline__ void zero_tail_rows(uint8_t* stage_buf, int chunks, i
   fence_proxy_async_smem();
 }
 
-template <bool KRAGGED, typename TOut>
+// SWIGLU (row-ragged mode): B holds [gate | up], 2 N columns per group; the leader CTA loads the
+// tile's 128 gate columns, its peer the matching 128 up columns, so that every accumulator row holds
+// gate in columns 0..127 and up in 128..255, and the stored tile is 256 x 128.
+template <bool KRAGGED, typename TOut, bool SWIGLU = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFastThreads, 1)
 gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                       const FastParams fp) {
@@ -78,6 +81,8 @@ gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   uint8_t* epi_stage = smem + kPairStages * kPairStageBytes + ((sizeof(PairSmemTail) + 15) & ~size_t(15));
   volatile int* abort_flag = &tail.abort_flag;
 
+  constexpr int BNT = SWIGLU ? kBN / 2 : kBN;  // output columns per tile
+  static_assert(!SWIGLU || !KRAGGED, "the fused activation exists for row-ragged problems");
   const CanonProblem& p = fp.p;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -105,7 +110,7 @@ gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     tmem_alloc_pair(&tail.tmem_base, kTmemCols);
     tmem_relinquish_pair();
   }
-  sched_init<kPairBM, kBN>(p, tail.sched);
+  sched_init<kPairBM, BNT>(p, tail.sched);
   tcgen05_fence_before_sync();
   cluster_sync_all();  // barriers of both CTAs are initialised before anyone signals across
   tcgen05_fence_after_sync();
@@ -123,12 +128,12 @@ gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       for (int round = 0; ok; ++round) {
         const int t = tile_of_round<KRAGGED>(round, pair, n_pairs);
         if (t >= total) break;
-        const TileInfo ti = decode_tile<kPairBM, kBN>(p, tail.sched, t);
+        const TileInfo ti = decode_tile<kPairBM, BNT>(p, tail.sched, t);
         const int nkb = (ti.klen + kBK - 1) / kBK;
         const int az = a_batched ? ti.g : 0;
         const int bz = KRAGGED ? 0 : ti.g;
         const int row0 = ti.m0 + int(rank) * 128;
-        const int col0 = ti.n0 + int(rank) * kPairBNHalf;
+        const int col0 = SWIGLU ? (rank ? p.N + ti.n0 : ti.n0) : ti.n0 + int(rank) * kPairBNHalf;
         for (int kb = 0; kb < nkb; ++kb) {
           if (!mbar_wait(&tail.empty[s], ph ^ 1, abort_flag)) {
             atomicCAS(p.status, 0, ST_PAIR_PRODUCER_TIMEOUT);
@@ -265,7 +270,7 @@ gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     for (; ok; ++it) {
       const int t = tile_of_round<KRAGGED>(it, pair, n_pairs);
       if (t >= total) break;
-      const TileInfo ti = decode_tile<kPairBM, kBN>(p, tail.sched, t);
+      const TileInfo ti = decode_tile<kPairBM, BNT>(p, tail.sched, t);
       const int buf = it & 1;
       const uint32_t aph = (it >> 1) & 1;
       if (!mbar_wait(&tail.acc_full[buf], aph, abort_flag, kEpilogueBackoffNs)) {
@@ -278,11 +283,16 @@ gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       TOut* c_warp = c_base + (long long)ti.g * p.c_sg + (long long)(ti.m0 + row0) * p.c_sm +
                      (long long)ti.n0 * p.c_sn;
       const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + buf * kBN;
-      const int ncols_tile = min(kBN, p.N - ti.n0);
+      const int ncols_tile = min(BNT, p.N - ti.n0);
       // A warp whose rows lie wholly past the group's end has nothing to read or store.
-      if (row0 < ti.rows)
-        epilogue_store_warp<TOut>(t_row, c_warp, p.c_sm, p.c_sn, ti.rows - row0, ncols_tile,
-                                  epi_stage + (warp - 2) * kWarpStageBytes, KRAGGED && ti.klen == 0, lane);
+      if (row0 < ti.rows) {
+        if constexpr (SWIGLU)
+          epilogue_store_warp_swiglu<TOut>(t_row, c_warp, p.c_sm, p.c_sn, ti.rows - row0, ncols_tile,
+                                           epi_stage + (warp - 2) * kWarpStageBytes, lane);
+        else
+          epilogue_store_warp<TOut>(t_row, c_warp, p.c_sm, p.c_sn, ti.rows - row0, ncols_tile,
+                                    epi_stage + (warp - 2) * kWarpStageBytes, KRAGGED && ti.klen == 0, lane);
+      }
       tcgen05_fence_before_sync();
       mbar_arrive_cluster(map_to_cta(smem_u32(&tail.acc_empty[buf]), 0));
     }

@@ -100,7 +100,7 @@ __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* tmap) {
 }
 
 // Loads one box whose first element is (x, y, z) — x is the innermost coordinate and must be
-// a multiple of 8 elements for 16-bit types. Out-of-range elements arrive as zeros and the
+// a multiple of 16 bytes (8 16-bit or 4 32-bit elements). Out-of-range elements arrive as zeros and the
 // full box byte count is always signalled on `bar`.
 __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* tmap, uint64_t* bar, int x,
                                             int y, int z) {

@@ -2,7 +2,9 @@
 
 ``route`` turns per-token expert choices into the int32 END offsets ``grouped_mm`` takes as
 ``offs`` plus the row permutation; ``permute`` gathers token rows into group-contiguous order;
-``combine`` sums each token's ``topk`` expert outputs back, weighted. The reference shows only the
+``combine`` sums each token's ``topk`` expert outputs back, weighted; ``gated_up_projection`` is the
+feed-forward block's first half, ``silu(x @ gate) * (x @ up)``, with the activation fused into the
+grouped GEMM's epilogue. The reference shows only the
 offsets half of ``route``, on the host, in its benchmark (bench/bench_2d3d.py:131-138:
 ``bincount`` then ``cumsum``). Everything here runs in CUDA kernels of the same library, on the
 current stream, with no host synchronisation; there is no CPU path.
@@ -14,8 +16,9 @@ from typing import Optional, Tuple
 
 import torch
 
-from . import _lib
+from . import _lib, _op
 from ._op import _DTYPES
+from .api import grouped_mm, output_geometry
 
 
 def _check(lib, rc: int) -> None:
@@ -90,4 +93,52 @@ def combine(y: torch.Tensor, inv_perm: torch.Tensor, weights: Optional[torch.Ten
         _check(lib, lib.gmm_combine_rows(y.data_ptr(), _DTYPES[y.dtype], y.stride(0), inv_perm.data_ptr(), w_ptr, topk,
                                          n_tokens, y.size(1), out.data_ptr(), _DTYPES[out_dtype], out.stride(0),
                                          _stream(y.device)))
+    return out
+
+
+def gated_up_projection(x: torch.Tensor, gate_up: torch.Tensor, offs: torch.Tensor,
+                        out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """``out[rows_g] = silu(x[rows_g] @ gate[g]) * (x[rows_g] @ up[g])`` for every group ``g``.
+
+    ``x`` ``[M_total, K]`` holds the token rows in group order (see ``permute``), ``gate_up``
+    ``[G, K, 2N]`` each expert's gate weights in columns ``[0, N)`` and up weights in ``[N, 2N)``,
+    ``offs`` the int32 END offsets. Returns ``[M_total, N]`` of ``out_dtype`` (default: ``x.dtype``;
+    float32 also allowed); rows at or past ``offs[-1]`` are left uninitialised, as with ``grouped_mm``.
+
+    Both products accumulate in fp32 and the activation is applied to the fp32 accumulators inside
+    the GEMM kernel, so the ``[M_total, 2N]`` intermediate is neither written nor read back and the
+    result is rounded once. Forward only (inference): inputs that require grad are rejected. The
+    reference has no such op; its users call ``grouped_mm`` and an element-wise kernel.
+
+    Operands the tensor-core path cannot address (fp32, unaligned pitches, odd ``N`` with a row-major
+    ``gate_up``) are multiplied by ``grouped_mm`` into an fp32 intermediate and activated by torch
+    kernels on the GPU instead: same values, one more pass over memory.
+    """
+    if not (x.is_cuda and gate_up.is_cuda and offs.is_cuda):
+        raise RuntimeError("grouped_mm_b200.moe is GPU-only; CPU tensors are not supported")
+    if x.dim() != 2 or gate_up.dim() != 3 or x.size(1) != gate_up.size(1):
+        raise RuntimeError("gated_up_projection expects x [M_total, K] and gate_up [G, K, 2N]")
+    if gate_up.size(2) % 2:
+        raise RuntimeError("gate_up needs an even number of columns: [gate | up]")
+    if x.dtype != gate_up.dtype:
+        raise RuntimeError("x and gate_up must have the same dtype")
+    if offs.dtype != torch.int32 or offs.dim() != 1 or offs.numel() != gate_up.size(0):
+        raise RuntimeError("offs has to be a 1D int32 tensor with one END offset per group")
+    if torch.is_grad_enabled() and (x.requires_grad or gate_up.requires_grad):
+        raise RuntimeError("gated_up_projection is forward-only; call it under torch.no_grad() or use grouped_mm")
+    out_dtype = out_dtype or x.dtype
+    if out_dtype not in (x.dtype, torch.float32):
+        raise RuntimeError("out_dtype must be the input dtype or float32")
+    n = gate_up.size(2) // 2
+    size, strides = output_geometry((x.size(0), x.size(1)), (gate_up.size(0), x.size(1), n), offs.numel(),
+                                    out_dtype.itemsize)
+    out = torch.empty_strided(size, strides, device=x.device, dtype=out_dtype)
+    if out.numel() == 0:
+        return out
+    if x.size(1) == 0:
+        return out.zero_()  # silu(0) * 0
+    if _op.grouped_mm_2d3d_swiglu(x, gate_up, offs, out):
+        return out
+    both = grouped_mm(x, gate_up, offs=offs, out_dtype=torch.float32)
+    torch.mul(torch.nn.functional.silu(both[:, :n]), both[:, n:], out=out)
     return out

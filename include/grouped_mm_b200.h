@@ -35,7 +35,8 @@ enum gmm_status {
   GMM_ERR_WORKSPACE = -4,        /* workspace missing, misaligned or smaller than gmm_workspace_bytes() */
   GMM_ERR_CUDA = -5,             /* a CUDA runtime/driver call failed; see gmm_last_cuda_error() */
   GMM_ERR_NOT_SM100 = -6,        /* the current device is not compute capability 10.x */
-  GMM_ERR_DEVICE_WAIT = -7       /* a bounded wait inside a kernel gave up (reported by gmm_check_status) */
+  GMM_ERR_DEVICE_WAIT = -7,      /* a bounded wait inside a kernel gave up (reported by gmm_check_status) */
+  GMM_ERR_NOT_FUSABLE = -8       /* grouped_mm_2d3d_swiglu: operands the tensor-core path cannot address */
 };
 
 /* Which kernel a call is routed to. */
@@ -118,6 +119,22 @@ int grouped_mm_2d3d(const gmm_tensor_t* a, const gmm_tensor_t* b, const int32_t*
  */
 int grouped_mm_3d2d(const gmm_tensor_t* a, const gmm_tensor_t* b, const int32_t* offs, int32_t n_groups,
                     const gmm_tensor_t* out, const gmm_launch_t* launch);
+
+/*
+ * The gated up-projection of an MoE feed-forward block in one pass:
+ *   out[r,:] = silu(a[r,:] @ gate[g(r)]) * (a[r,:] @ up[g(r)])
+ * with b_gate_up [G,K,2N] holding gate in columns [0,N) and up in [N,2N) of every group (the usual
+ * fused "gate_up" weight), a [M_total,K], out [M_total,N], offs as for grouped_mm_2d3d. Both
+ * products accumulate in fp32 and the activation is evaluated on the fp32 accumulators, so the
+ * result is rounded once; the [M_total,2N] intermediate never reaches memory.
+ *
+ * No counterpart in the reference, whose callers run grouped_mm_2d3d and then an element-wise
+ * kernel. Tensor-core path only: 16-bit operands, 16-byte aligned bases and pitches, row-major a,
+ * N a multiple of 8 when b is row-major. Anything else returns GMM_ERR_NOT_FUSABLE and launches
+ * nothing; the caller then uses grouped_mm_2d3d followed by its own activation.
+ */
+int grouped_mm_2d3d_swiglu(const gmm_tensor_t* a, const gmm_tensor_t* b_gate_up, const int32_t* offs,
+                           int32_t n_groups, const gmm_tensor_t* out, const gmm_launch_t* launch);
 
 /*
  * grouped_mm_2d3d() for callers that cannot provide a workspace because they cannot allocate

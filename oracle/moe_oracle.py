@@ -40,3 +40,23 @@ def combine_oracle(y: torch.Tensor, inv_perm: torch.Tensor, weights: Optional[to
     w = torch.ones(inv.shape) if weights is None else weights.detach().cpu().float().view(-1, topk)
     w = torch.where(inv >= 0, w, torch.zeros_like(w))
     return (yy[inv.clamp_min(0)] * w.unsqueeze(-1)).sum(1)
+
+
+def gated_up_oracle(x: torch.Tensor, gate_up: torch.Tensor, offs: torch.Tensor):
+    """``silu(x_g @ gate_g) * (x_g @ up_g)`` per group in fp32 on the CPU, with ``gate_up[g]`` holding
+    ``[gate | up]`` side by side. No counterpart in the reference (its callers apply the activation
+    after ``grouped_mm``, whose per-group product this restates as in grouped_mm_oracle). Returns
+    ``(out [M_total, N] fp32, defined [M_total] bool)``: rows at or past ``offs[-1]`` are undefined."""
+    xx, ww = x.detach().cpu().float(), gate_up.detach().cpu().float()
+    n = ww.size(2) // 2
+    ends = [max(0, min(int(e), xx.size(0))) for e in offs.detach().cpu().tolist()]
+    out = torch.zeros((xx.size(0), n), dtype=torch.float32)
+    defined = torch.zeros(xx.size(0), dtype=torch.bool)
+    start = 0
+    for g, end in enumerate(ends):
+        if end > start:
+            both = xx[start:end] @ ww[g]
+            out[start:end] = torch.nn.functional.silu(both[:, :n]) * both[:, n:]
+            defined[start:end] = True
+        start = max(start, end)
+    return out, defined
