@@ -18,7 +18,7 @@ import torch
 
 from . import _lib, _op
 from ._op import _DTYPES
-from .api import grouped_mm, output_geometry
+from .api import forward_into, output_geometry
 
 
 def _check(lib, rc: int) -> None:
@@ -96,6 +96,59 @@ def combine(y: torch.Tensor, inv_perm: torch.Tensor, weights: Optional[torch.Ten
     return out
 
 
+def _gated_up_forward(x: torch.Tensor, gate_up: torch.Tensor, offs: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    n = gate_up.size(2) // 2
+    size, strides = output_geometry((x.size(0), x.size(1)), (gate_up.size(0), x.size(1), n), offs.numel(),
+                                    out_dtype.itemsize)
+    out = torch.empty_strided(size, strides, device=x.device, dtype=out_dtype)
+    if out.numel() == 0:
+        return out
+    if x.size(1) == 0:
+        return out.zero_()  # silu(0) * 0
+    if _op.grouped_mm_2d3d_swiglu(x, gate_up, offs, out):
+        return out
+    both = torch.empty((x.size(0), 2 * n), dtype=torch.float32, device=x.device)
+    forward_into(x, gate_up, offs, both)
+    torch.mul(torch.nn.functional.silu(both[:, :n]), both[:, n:], out=out)
+    return out
+
+
+class _GatedUp(torch.autograd.Function):
+    """Keeps only the inputs: the backward pass recomputes both products (one grouped GEMM with an
+    fp32 result) instead of storing the ``[M_total, 2N]`` pre-activations the forward never wrote."""
+
+    @staticmethod
+    def forward(ctx, x, gate_up, offs, out_dtype):  # type: ignore[override]
+        ctx.save_for_backward(x, gate_up, offs)
+        return _gated_up_forward(x, gate_up, offs, out_dtype)
+
+    @staticmethod
+    def backward(ctx, grad_out):  # type: ignore[override]
+        x, gate_up, offs = ctx.saved_tensors
+        need_x, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        if grad_out.numel() == 0 or x.size(1) == 0:
+            return (torch.zeros_like(x) if need_x else None, torch.zeros_like(gate_up) if need_w else None, None, None)
+        n = gate_up.size(2) // 2
+        # Rows at or past offs[-1] belong to no group: zeros there give zero gradients.
+        both = torch.zeros((x.size(0), 2 * n), dtype=torch.float32, device=x.device)
+        forward_into(x, gate_up, offs, both)
+        gate, up = both[:, :n], both[:, n:]
+        sig = torch.sigmoid(gate)
+        dy = grad_out.float()
+        d_both = torch.empty((x.size(0), 2 * n), dtype=x.dtype, device=x.device)
+        d_both[:, :n] = dy * up * sig * (1.0 + gate * (1.0 - sig))  # d silu(g)/dg = s (1 + g (1 - s))
+        d_both[:, n:] = dy * gate * sig
+        del both, sig, dy
+        grad_x = grad_w = None
+        if need_x:  # dX[rows_g] = dBoth[rows_g] @ W[g]^T  (2D x 3D)
+            grad_x = torch.zeros_like(x)
+            forward_into(d_both, gate_up.transpose(-2, -1), offs, grad_x)
+        if need_w:  # dW[g] = X[rows_g]^T @ dBoth[rows_g]  (2D x 2D; empty groups give zeros)
+            grad_w = torch.empty_like(gate_up)
+            forward_into(x.transpose(-2, -1), d_both, offs, grad_w)
+        return grad_x, grad_w, None, None
+
+
 def gated_up_projection(x: torch.Tensor, gate_up: torch.Tensor, offs: torch.Tensor,
                         out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """``out[rows_g] = silu(x[rows_g] @ gate[g]) * (x[rows_g] @ up[g])`` for every group ``g``.
@@ -107,12 +160,13 @@ def gated_up_projection(x: torch.Tensor, gate_up: torch.Tensor, offs: torch.Tens
 
     Both products accumulate in fp32 and the activation is applied to the fp32 accumulators inside
     the GEMM kernel, so the ``[M_total, 2N]`` intermediate is neither written nor read back and the
-    result is rounded once. Forward only (inference): inputs that require grad are rejected. The
-    reference has no such op; its users call ``grouped_mm`` and an element-wise kernel.
+    result is rounded once. Differentiable: the backward pass recomputes the two products rather
+    than keeping them (three more grouped GEMMs: the recompute, dX and dW). The reference has no such
+    op; its users call ``grouped_mm`` and an element-wise kernel.
 
     Operands the tensor-core path cannot address (fp32, unaligned pitches, odd ``N`` with a row-major
-    ``gate_up``) are multiplied by ``grouped_mm`` into an fp32 intermediate and activated by torch
-    kernels on the GPU instead: same values, one more pass over memory.
+    ``gate_up``) are multiplied by the ordinary grouped GEMM into an fp32 intermediate and activated by
+    torch kernels on the GPU instead: same values, one more pass over memory.
     """
     if not (x.is_cuda and gate_up.is_cuda and offs.is_cuda):
         raise RuntimeError("grouped_mm_b200.moe is GPU-only; CPU tensors are not supported")
@@ -122,23 +176,13 @@ def gated_up_projection(x: torch.Tensor, gate_up: torch.Tensor, offs: torch.Tens
         raise RuntimeError("gate_up needs an even number of columns: [gate | up]")
     if x.dtype != gate_up.dtype:
         raise RuntimeError("x and gate_up must have the same dtype")
+    if x.dtype not in _DTYPES:
+        raise RuntimeError(f"Expected x to be Float32, BFloat16 or Float16 matrix, got {x.dtype}")
     if offs.dtype != torch.int32 or offs.dim() != 1 or offs.numel() != gate_up.size(0):
         raise RuntimeError("offs has to be a 1D int32 tensor with one END offset per group")
-    if torch.is_grad_enabled() and (x.requires_grad or gate_up.requires_grad):
-        raise RuntimeError("gated_up_projection is forward-only; call it under torch.no_grad() or use grouped_mm")
+    if offs.numel() >= 1024:
+        raise RuntimeError("Can't process more than 1024 groups")
     out_dtype = out_dtype or x.dtype
     if out_dtype not in (x.dtype, torch.float32):
         raise RuntimeError("out_dtype must be the input dtype or float32")
-    n = gate_up.size(2) // 2
-    size, strides = output_geometry((x.size(0), x.size(1)), (gate_up.size(0), x.size(1), n), offs.numel(),
-                                    out_dtype.itemsize)
-    out = torch.empty_strided(size, strides, device=x.device, dtype=out_dtype)
-    if out.numel() == 0:
-        return out
-    if x.size(1) == 0:
-        return out.zero_()  # silu(0) * 0
-    if _op.grouped_mm_2d3d_swiglu(x, gate_up, offs, out):
-        return out
-    both = grouped_mm(x, gate_up, offs=offs, out_dtype=torch.float32)
-    torch.mul(torch.nn.functional.silu(both[:, :n]), both[:, n:], out=out)
-    return out
+    return _GatedUp.apply(x, gate_up, offs, out_dtype)
