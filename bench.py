@@ -362,6 +362,9 @@ def main():
                     help="shrink the ragged extent (routed rows) of the workload; for small profiling cases only")
     ap.add_argument("--no-baselines", action="store_true", help="skip the CPU and Triton baseline legs")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--tf32", action="store_true",
+                    help="fp32 operands multiplied as TF32 (torch.backends.cuda.matmul.allow_tf32 = True) instead of "
+                         "the benchmark's bf16; a side measurement, reported against half the bf16 tensor peak")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -374,7 +377,14 @@ def main():
     peaks = read_peaks()
 
     # Every rank owns its own experts (weak scaling): same shape, its own seeded draw.
-    wl = make_workload(args.workload, dev, seed=rank, scale=args.rows_scale, dims_scale=args.dims_scale)
+    if args.tf32:
+        torch.backends.cuda.matmul.allow_tf32 = True
+        args.no_baselines = True  # the CPU and Triton legs are for the bf16 benchmark
+        peaks = dict(peaks, tflops=peaks["tflops"] / 2,
+                     tflops_sustained=peaks["tflops_sustained"] / 2 if peaks["tflops_sustained"] else None,
+                     source=peaks["source"] + "; TF32 peak taken as half the bf16 figure")
+    wl = make_workload(args.workload, dev, seed=rank, scale=args.rows_scale, dims_scale=args.dims_scale,
+                       dtype=torch.float32 if args.tf32 else torch.bfloat16)
     from grouped_mm_bf16_b200 import _lib, _op
 
     out = call_operator(wl)
@@ -403,10 +413,10 @@ def main():
         roofline = {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                     "frac": gbs / peaks["hbm_gbs"]}
     roofline.update({
-        "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
+        "traffic": None if args.tf32 else NCU_TRAFFIC_BYTES.get(args.workload),
         "peak_source": f"{peaks['source']} (burst cuBLAS bf16 / copy bandwidth)",
         "frac_of_sustained_peak": (achieved / peaks["tflops_sustained"]) if peaks["tflops_sustained"] else None,
-        "frac_of_nominal_2250": achieved / 2250.0,
+        "frac_of_nominal_2250": None if args.tf32 else achieved / 2250.0,
         "algorithmic_flops_per_launch": wl.flops, "algorithmic_bytes_per_launch": wl.algorithmic_bytes,
         "kernel": {1: "gmm_sm100_kernel (TMA + tcgen05.mma, one CTA per 128x256 tile)", 2: "gmm_generic_kernel",
                    3: "gmm_sm100_pair_kernel (TMA + tcgen05.mma.cta_group::2, CTA pair per 256x256 tile)"}.get(kernel, "none"),
@@ -456,7 +466,8 @@ def main():
             lo, hi = partition_groups(sizes, world)[rank]
             local_sizes = sizes[lo:hi]
             if sum(local_sizes) > 0:
-                swl = make_workload(args.workload, dev, seed=0, sizes=local_sizes)
+                swl = make_workload(args.workload, dev, seed=0, sizes=local_sizes,
+                                    dtype=torch.float32 if args.tf32 else torch.bfloat16)
                 s_ms = time_steps(dist, lambda: call_operator(swl), args.steps, args.warmup)
                 s_flops = swl.flops
             else:
@@ -472,7 +483,9 @@ def main():
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "bf16 in/out, f32 accumulate", "data": "synthetic",
+            "vs_baseline": None,
+            "dtype": "fp32 in/out multiplied as TF32, f32 accumulate (NOT the benchmark dtype)" if args.tf32
+            else "bf16 in/out, f32 accumulate", "data": "synthetic",
             "config": {
                 "workload": f"{args.workload}: form {wl.form}, a {tuple(wl.mat_a.shape)}, b {tuple(wl.mat_b.shape)}, "
                             f"{len(wl.sizes) if wl.sizes else wl.mat_a.size(0)} groups per GPU, seeded sizes",
