@@ -82,6 +82,8 @@ int init_device(int dev) {
     if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_kernel<true, float>);
     if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_kernel<false, float, 4>);
     if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_kernel<true, float, 4>);
+    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_pair_kernel<false, float, false, 4>, kPairSmemBytes);
+    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_pair_kernel<true, float, false, 4>, kPairSmemBytes);
     if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_kernel<false, __nv_bfloat16, 2, true>);
     if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_kernel<false, __half, 2, true>);
     if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_kernel<false, float, 2, true>);
@@ -247,7 +249,7 @@ FastPlan plan_fast(const CanonProblem& p, uint32_t flags, bool swiglu = false) {
   f.ok = true;
   // 256-row pair tiles pay off when groups are tall (little tail waste) and N spans both halves.
   // The group sizes live on the device, so the host decides on the mean rows per group.
-  if ((p.N > kPairBNHalf || swiglu) && !tf32) {
+  if (p.N > kPairBNHalf || swiglu) {
     const long long mean_rows = (p.mode == MODE_MRAGGED) ? (long long)p.M / (p.G > 0 ? p.G : 1) : p.M;
     f.pair = mean_rows >= 768;
     if (flags & GMM_FLAG_FORCE_PAIR) f.pair = true;
@@ -433,20 +435,26 @@ int launch_fast(const CanonProblem& p_in, const FastPlan& plan, const DeviceInfo
       default: return launch_swiglu_t<float>(ta, tb, fp, plan.pair, grid, st);
     }
   }
+  if (tf32) {
+    if (plan.pair) {
+      if (p.mode == MODE_KRAGGED)
+        gmm_sm100_pair_kernel<true, float, false, 4><<<grid, kFastThreads, kPairSmemBytes, st>>>(ta, tb, fp);
+      else
+        gmm_sm100_pair_kernel<false, float, false, 4><<<grid, kFastThreads, kPairSmemBytes, st>>>(ta, tb, fp);
+    } else if (p.mode == MODE_KRAGGED) {
+      gmm_sm100_kernel<true, float, 4><<<grid, kFastThreads, kFastSmemBytes, st>>>(ta, tb, fp);
+    } else {
+      gmm_sm100_kernel<false, float, 4><<<grid, kFastThreads, kFastSmemBytes, st>>>(ta, tb, fp);
+    }
+    GMM_CUDA_TRY(cudaGetLastError());
+    return GMM_OK;
+  }
   if (plan.pair) {
     switch (p.out_dtype) {
       case DT_BF16: return launch_pair_t<__nv_bfloat16>(ta, tb, fp, grid, st);
       case DT_F16: return launch_pair_t<__half>(ta, tb, fp, grid, st);
       default: return launch_pair_t<float>(ta, tb, fp, grid, st);
     }
-  }
-  if (tf32) {
-    if (p.mode == MODE_KRAGGED)
-      gmm_sm100_kernel<true, float, 4><<<grid, kFastThreads, kFastSmemBytes, st>>>(ta, tb, fp);
-    else
-      gmm_sm100_kernel<false, float, 4><<<grid, kFastThreads, kFastSmemBytes, st>>>(ta, tb, fp);
-    GMM_CUDA_TRY(cudaGetLastError());
-    return GMM_OK;
   }
   return p.mode == MODE_KRAGGED ? launch_fast_kr<true>(ta, tb, fp, grid, st)
                                 : launch_fast_kr<false>(ta, tb, fp, grid, st);

@@ -54,13 +54,15 @@ enum PairStatus : int {
   ST_PAIR_RELAY_TIMEOUT = 0x204,
 };
 
-// Zeroes k-rows [r, 64) of `chunks` MN-major chunks (each [64 k-rows][128 B]) of one stage buffer.
+// Zeroes k-rows [r, BK) of the MN-major chunks (each [BK k-rows][128 B]) of one 16 KiB stage buffer.
 // Whole-warp call; ends with the proxy fence that makes the zeros visible to the MMA.
-__device__ __forceinline__ void zero_tail_rows(uint8_t* stage_buf, int chunks, int r, int lane) {
-  const int n16 = (kBK - r) * 8;  // 16-byte words per chunk
+template <int ES>
+__device__ __forceinline__ void zero_tail_rows(uint8_t* stage_buf, int r, int lane) {
+  using EG = ElemGeom<ES>;
+  const int n16 = (EG::BK - r) * 8;  // 16-byte words per chunk
   const uint4 z = make_uint4(0, 0, 0, 0);
-  for (int c = 0; c < chunks; ++c) {
-    uint4* q = reinterpret_cast<uint4*>(stage_buf + c * kChunkBytes + r * 128);
+  for (int c = 0; c < 128 / EG::CHUNK_W; ++c) {
+    uint4* q = reinterpret_cast<uint4*>(stage_buf + c * EG::CHUNK_BYTES + r * 128);
     for (int i = lane; i < n16; i += 32) q[i] = z;
   }
   fence_proxy_async_smem();
@@ -69,7 +71,8 @@ __device__ __forceinline__ void zero_tail_rows(uint8_t* stage_buf, int chunks, i
 // SWIGLU (row-ragged mode): B holds [gate | up], 2 N columns per group; the leader CTA loads the
 // tile's 128 gate columns, its peer the matching 128 up columns, so that every accumulator row holds
 // gate in columns 0..127 and up in 128..255, and the stored tile is 256 x 128.
-template <bool KRAGGED, typename TOut, bool SWIGLU = false>
+// ES: operand element size, 2 (bf16/fp16) or 4 (fp32 read as TF32), as in the single-CTA kernel.
+template <bool KRAGGED, typename TOut, bool SWIGLU = false, int ES = 2>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFastThreads, 1)
 gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                       const FastParams fp) {
@@ -81,8 +84,11 @@ gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   uint8_t* epi_stage = smem + kPairStages * kPairStageBytes + ((sizeof(PairSmemTail) + 15) & ~size_t(15));
   volatile int* abort_flag = &tail.abort_flag;
 
+  using EG = ElemGeom<ES>;
+  constexpr int BK = EG::BK;
+  constexpr int kChunks = 128 / EG::CHUNK_W;   // MN-major chunks per 128-wide operand half
   constexpr int BNT = SWIGLU ? kBN / 2 : kBN;  // output columns per tile
-  static_assert(!SWIGLU || !KRAGGED, "the fused activation exists for row-ragged problems");
+  static_assert(!SWIGLU || (!KRAGGED && ES == 2), "the fused activation exists for 16-bit row-ragged problems");
   const CanonProblem& p = fp.p;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -129,7 +135,7 @@ gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         const int t = tile_of_round<KRAGGED>(round, pair, n_pairs);
         if (t >= total) break;
         const TileInfo ti = decode_tile<kPairBM, BNT>(p, tail.sched, t);
-        const int nkb = (ti.klen + kBK - 1) / kBK;
+        const int nkb = (ti.klen + BK - 1) / BK;
         const int az = a_batched ? ti.g : 0;
         const int bz = KRAGGED ? 0 : ti.g;
         const int row0 = ti.m0 + int(rank) * 128;
@@ -148,7 +154,7 @@ gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             if (rank == 0) mbar_arrive_expect_tx(&tail.full[s], 2 * kPairStageBytes);
             bar = map_to_cta(smem_u32(&tail.full[s]), 0);
           }
-          const int k = ti.k0 + kb * kBK;
+          const int k = ti.k0 + kb * BK;
           uint8_t* sa = smem_a + s * kPairAStageBytes;
           uint8_t* sb = smem_b + s * kPairBStageBytes;
           auto load_a = [&](void* dst, int x, int y) { tma_load_3d_pair(dst, &tmap_a, bar, x, y, az); };
@@ -157,13 +163,13 @@ gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             load_a(sa, k, row0);
           } else {
 #pragma unroll
-            for (int c = 0; c < 2; ++c) load_a(sa + c * kChunkBytes, row0 + c * 64, k);
+            for (int c = 0; c < kChunks; ++c) load_a(sa + c * EG::CHUNK_BYTES, row0 + c * EG::CHUNK_W, k);
           }
           if (!fp.b_mn) {
             load_b(sb, k, col0);
           } else {
 #pragma unroll
-            for (int c = 0; c < 2; ++c) load_b(sb + c * kChunkBytes, col0 + c * 64, k);
+            for (int c = 0; c < kChunks; ++c) load_b(sb + c * EG::CHUNK_BYTES, col0 + c * EG::CHUNK_W, k);
           }
           if (++s == kPairStages) { s = 0; ph ^= 1; }
         }
@@ -172,10 +178,15 @@ gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (leader CTA, lane 0)
     if (rank == 0) {
-      const uint32_t a_lbo = fp.a_mn ? kChunkBytes : 16;
-      const uint32_t b_lbo = fp.b_mn ? kChunkBytes : 16;
-      const uint32_t a_kstep = fp.a_mn ? (kUmmaK * 128) : (kUmmaK * 2);
-      const uint32_t b_kstep = fp.b_mn ? (kUmmaK * 128) : (kUmmaK * 2);
+      // descriptor geometry: see the single-CTA kernel
+      const uint32_t a_lbo = fp.a_mn ? EG::CHUNK_BYTES : 16;
+      const uint32_t b_lbo = fp.b_mn ? EG::CHUNK_BYTES : 16;
+      const uint32_t a_kstep = fp.a_mn ? (EG::UMMA_K * 128) : 32;
+      const uint32_t b_kstep = fp.b_mn ? (EG::UMMA_K * 128) : 32;
+      const uint32_t a_sbo = (ES == 4 && fp.a_mn) ? 512 : 1024;
+      const uint32_t b_sbo = (ES == 4 && fp.b_mn) ? 512 : 1024;
+      const uint32_t a_swz = (ES == 4 && fp.a_mn) ? kSwizzle128BBase32B : kSwizzle128B;
+      const uint32_t b_swz = (ES == 4 && fp.b_mn) ? kSwizzle128BBase32B : kSwizzle128B;
       int s = 0;
       uint32_t ph = 0;
       int it = 0;
@@ -184,7 +195,7 @@ gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         const int t = tile_of_round<KRAGGED>(it, pair, n_pairs);
         if (t >= total) break;
         const int klen = tile_klen(p, tail.sched, t);  // the issuer needs no tile coordinates
-        const int nkb = (klen + kBK - 1) / kBK;
+        const int nkb = (klen + BK - 1) / BK;
         const int buf = it & 1;
         const uint32_t aph = (it >> 1) & 1;
         if (!mbar_wait_cluster(&tail.acc_empty[buf], aph ^ 1, abort_flag)) {
@@ -201,10 +212,10 @@ gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             break;
           }
           if constexpr (KRAGGED) {
-            const int r = klen - kb * kBK;
-            if (r < kBK) {
-              zero_tail_rows(smem_a + s * kPairAStageBytes, 2, r, lane);
-              zero_tail_rows(smem_b + s * kPairBStageBytes, 2, r, lane);
+            const int r = klen - kb * BK;
+            if (r < BK) {
+              zero_tail_rows<ES>(smem_a + s * kPairAStageBytes, r, lane);
+              zero_tail_rows<ES>(smem_b + s * kPairBStageBytes, r, lane);
             }
             __syncwarp();
             if (!mbar_wait_cluster(&tail.peer_ready[s], ph, abort_flag)) {
@@ -215,12 +226,18 @@ gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           }
           tcgen05_fence_after_sync();
           if (lane == 0) {
-            const uint64_t a_desc = make_smem_desc_sw128(smem_u32(smem_a + s * kPairAStageBytes), a_lbo, 1024);
-            const uint64_t b_desc = make_smem_desc_sw128(smem_u32(smem_b + s * kPairBStageBytes), b_lbo, 1024);
+            const uint64_t a_desc =
+                make_smem_desc_sw128(smem_u32(smem_a + s * kPairAStageBytes), a_lbo, a_sbo, a_swz);
+            const uint64_t b_desc =
+                make_smem_desc_sw128(smem_u32(smem_b + s * kPairBStageBytes), b_lbo, b_sbo, b_swz);
 #pragma unroll
-            for (int k = 0; k < kBK / kUmmaK; ++k) {
-              umma_f16_ss_pair(d_tmem, a_desc + ((k * a_kstep) >> 4), b_desc + ((k * b_kstep) >> 4), fp.idesc,
-                               (kb | k) != 0 ? 1u : 0u);
+            for (int k = 0; k < BK / EG::UMMA_K; ++k) {
+              if constexpr (ES == 4)
+                umma_tf32_ss_pair(d_tmem, a_desc + ((k * a_kstep) >> 4), b_desc + ((k * b_kstep) >> 4), fp.idesc,
+                                  (kb | k) != 0 ? 1u : 0u);
+              else
+                umma_f16_ss_pair(d_tmem, a_desc + ((k * a_kstep) >> 4), b_desc + ((k * b_kstep) >> 4), fp.idesc,
+                                 (kb | k) != 0 ? 1u : 0u);
             }
             umma_commit_pair(&tail.empty[s], 0x3);  // frees the stage in both CTAs
           }
@@ -240,21 +257,21 @@ gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         const int t = tile_of_round<KRAGGED>(round, pair, n_pairs);
         if (t >= total) break;
         const int klen = tile_klen(p, tail.sched, t);
-        const int nkb = (klen + kBK - 1) / kBK;
+        const int nkb = (klen + BK - 1) / BK;
         for (int kb = 0; kb < nkb; ++kb) {
           if (!mbar_wait(&tail.full[s], ph, abort_flag)) {
             if (lane == 0) atomicCAS(p.status, 0, ST_PAIR_RELAY_TIMEOUT);
             ok = false;
             break;
           }
-          const int r = klen - kb * kBK;
-          if (r < kBK) {
-            zero_tail_rows(smem_a + s * kPairAStageBytes, 2, r, lane);
-            zero_tail_rows(smem_b + s * kPairBStageBytes, 2, r, lane);
+          const int r = klen - kb * BK;
+          if (r < BK) {
+            zero_tail_rows<ES>(smem_a + s * kPairAStageBytes, r, lane);
+            zero_tail_rows<ES>(smem_b + s * kPairBStageBytes, r, lane);
           }
           __syncwarp();
           if (lane == 0) {
-            if (r < kBK) mbar_arrive_cluster(ready_leader0 + s * (uint32_t)sizeof(uint64_t));
+            if (r < BK) mbar_arrive_cluster(ready_leader0 + s * (uint32_t)sizeof(uint64_t));
             else mbar_arrive_cluster_relaxed(ready_leader0 + s * (uint32_t)sizeof(uint64_t));
           }
           if (++s == kPairStages) { s = 0; ph ^= 1; }

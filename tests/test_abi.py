@@ -98,11 +98,12 @@ def test_fp32_takes_the_tcgen05_kernel_only_when_tf32_is_allowed(lib):
     a6 = _tensor((32, 62), (62, 1), _lib.GMM_F32)
     b6 = _tensor((6, 62, 44), (62 * 44, 44, 1), _lib.GMM_F32)
     assert _select(lib, _lib.FORM_2D3D, a6, b6, c4, _lib.GMM_FLAG_ALLOW_TF32) == _lib.GMM_KERNEL_GENERIC
-    # tall groups: 16-bit operands take the CTA-pair kernel, fp32 operands never do
+    # tall groups take the CTA-pair kernel, as with 16-bit operands
     at = _tensor((8192, 64), (64, 1), _lib.GMM_F32)
     bt = _tensor((2, 64, 512), (64 * 512, 512, 1), _lib.GMM_F32)
     ct = _tensor((8192, 512), (512, 1), _lib.GMM_F32)
-    flags = _lib.GMM_FLAG_ALLOW_TF32 | _lib.GMM_FLAG_FORCE_PAIR
+    assert _select(lib, _lib.FORM_2D3D, at, bt, ct, _lib.GMM_FLAG_ALLOW_TF32) == _lib.GMM_KERNEL_TCGEN05_PAIR
+    flags = _lib.GMM_FLAG_ALLOW_TF32 | _lib.GMM_FLAG_NO_PAIR
     assert _select(lib, _lib.FORM_2D3D, at, bt, ct, flags) == _lib.GMM_KERNEL_TCGEN05
     # the flag changes nothing for 16-bit operands
     a = _tensor((32, 64), (64, 1))

@@ -274,7 +274,7 @@ def _assert_tf32_parity(a, b, offs):
     with allow_tf32():
         out = grouped_mm(a, b, offs=offs)
         assert out.dtype == torch.float32
-        assert _op.selected_kernel(FORMS[_form(a, b)], a, b, out) == _lib.GMM_KERNEL_TCGEN05
+        assert _op.selected_kernel(FORMS[_form(a, b)], a, b, out) in _lib.TCGEN05_KINDS
     ref_t, defined = grouped_mm_oracle(_as_tf32(a), _as_tf32(b), offs)
     torch.testing.assert_close(out.cpu()[defined], ref_t[defined], atol=1e-3, rtol=1e-4)
     ref, _ = grouped_mm_oracle(a, b, offs)
@@ -286,7 +286,7 @@ def _assert_tf32_parity(a, b, offs):
 
 @pytest.mark.parametrize("a_col_major", [False, True])
 @pytest.mark.parametrize("b_col_major", [False, True])
-def test_tf32_3d3d_all_layouts(a_col_major, b_col_major):
+def test_tf32_3d3d_all_layouts(a_col_major, b_col_major, tile_kernel):
     g = torch.Generator(device=DEV).manual_seed(53)
     G, m, k, n = 3, 136, 200, 264
     a = torch.randn((G, k, m), device=DEV, generator=g).transpose(-2, -1) if a_col_major else \
@@ -298,7 +298,7 @@ def test_tf32_3d3d_all_layouts(a_col_major, b_col_major):
 
 @pytest.mark.parametrize("sizes", M_PATTERNS)
 @pytest.mark.parametrize("k,n,b_col_major", [(64, 48, False), (200, 264, False), (72, 520, True), (4, 4, True)])
-def test_tf32_2d3d_tile_boundaries(sizes, k, n, b_col_major):
+def test_tf32_2d3d_tile_boundaries(sizes, k, n, b_col_major, tile_kernel):
     g = torch.Generator(device=DEV).manual_seed(len(sizes) * 1000 + k + n + 1)
     a = torch.randn((sum(sizes), k), device=DEV, generator=g)
     if b_col_major:
@@ -312,7 +312,7 @@ def test_tf32_2d3d_tile_boundaries(sizes, k, n, b_col_major):
 
 @pytest.mark.parametrize("sizes", K_PATTERNS)
 @pytest.mark.parametrize("m,n", [(16, 24), (136, 264), (128, 256)])
-def test_tf32_2d2d_k_ragged(sizes, m, n):
+def test_tf32_2d2d_k_ragged(sizes, m, n, tile_kernel):
     g = torch.Generator(device=DEV).manual_seed(sum(sizes) + m + 1)
     kt = sum(sizes)
     a = torch.randn((kt, m), device=DEV, generator=g).t()  # column-major [M, K_total]
@@ -324,7 +324,7 @@ def test_tf32_2d2d_k_ragged(sizes, m, n):
 
 
 @pytest.mark.parametrize("sizes", [[7, 0, 1, 13, 11], [128, 130, 0, 60], [1, 0] * 10])
-def test_tf32_3d2d_n_ragged(sizes):
+def test_tf32_3d2d_n_ragged(sizes, tile_kernel):
     g = torch.Generator(device=DEV).manual_seed(59)
     m, k, nt = 40, 48, sum(sizes)
     a = torch.randn((len(sizes), m, k), device=DEV, generator=g)
@@ -350,7 +350,7 @@ def test_tf32_unaligned_operands_small_stay_generic_large_are_relaid_out():
         assert _op._worth_relayout(_lib.FORM_2D3D, a, b, out)
         a2, b2 = _op.tensor_core_layouts(_lib.FORM_2D3D, a, b)
         assert torch.equal(a2, a) and torch.equal(b2, b)
-        assert _op.selected_kernel(_lib.FORM_2D3D, a2, b2, out) == _lib.GMM_KERNEL_TCGEN05
+        assert _op.selected_kernel(_lib.FORM_2D3D, a2, b2, out) in _lib.TCGEN05_KINDS
     assert not _op._worth_relayout(_lib.FORM_2D3D, a, b, out)  # knob off again: fp32 stays true fp32
     ref_t, _ = grouped_mm_oracle(_as_tf32(a), _as_tf32(b), _offs(sizes))
     torch.testing.assert_close(out.cpu(), ref_t, atol=2e-3, rtol=1e-4)
