@@ -236,7 +236,8 @@ def run_reference_arm(args):
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     sizes = group_sizes(args.workload, 0)
-    wl = make_workload(args.workload, "cpu", seed=0, sizes=[min(s, 512) for s in sizes], dims_scale=args.dims_scale)
+    # Up to 4096 rows of every group: per-group GEMMs tall enough for the CPU BLAS to reach its best rate.
+    wl = make_workload(args.workload, "cpu", seed=0, sizes=[min(s, 4096) for s in sizes], dims_scale=args.dims_scale)
     per_step = max(1.0, min(8.0, 150.0 / max(1, args.steps + args.warmup)))
     times, flops, desc = [], 0.0, ""
     for i in range(args.warmup + args.steps):
