@@ -311,12 +311,12 @@ uint32_t make_idesc(int in_dtype, int a_mn, int b_mn, int mma_m) {
 
 // ------------------------------------------------------------------ launches
 
-template <typename TIn>
+template <typename TIn, int BM, int BN>
 int launch_generic_in(const CanonProblem& p, int grid, cudaStream_t st) {
   switch (p.out_dtype) {
-    case DT_BF16: gmm_generic_kernel<TIn, __nv_bfloat16><<<grid, kGenericThreads, 0, st>>>(p); break;
-    case DT_F16: gmm_generic_kernel<TIn, __half><<<grid, kGenericThreads, 0, st>>>(p); break;
-    default: gmm_generic_kernel<TIn, float><<<grid, kGenericThreads, 0, st>>>(p); break;
+    case DT_BF16: gmm_generic_kernel<TIn, __nv_bfloat16, BM, BN><<<grid, kGenericThreads, 0, st>>>(p); break;
+    case DT_F16: gmm_generic_kernel<TIn, __half, BM, BN><<<grid, kGenericThreads, 0, st>>>(p); break;
+    default: gmm_generic_kernel<TIn, float, BM, BN><<<grid, kGenericThreads, 0, st>>>(p); break;
   }
   GMM_CUDA_TRY(cudaGetLastError());
   return GMM_OK;
@@ -330,17 +330,29 @@ long long tile_upper_bound(const CanonProblem& p, int bm, int bn) {
   return mt * nt;
 }
 
+template <int BM, int BN>
+int launch_generic_tile(const CanonProblem& p, long long tiles, int blocks_per_sm, const DeviceInfo& d,
+                        cudaStream_t st) {
+  const long long cap = (long long)d.sm_count * blocks_per_sm;
+  const int grid = (int)(tiles < cap ? tiles : cap);
+  switch (p.in_dtype) {
+    case DT_BF16: return launch_generic_in<__nv_bfloat16, BM, BN>(p, grid, st);
+    case DT_F16: return launch_generic_in<__half, BM, BN>(p, grid, st);
+    default: return launch_generic_in<float, BM, BN>(p, grid, st);
+  }
+}
+
 int launch_generic(const CanonProblem& p, const DeviceInfo& d, cudaStream_t st) {
   const long long ub = tile_upper_bound(p, kGBM, kGBN);
   if (ub <= 0) return GMM_OK;
   if (ub > 0x7fffffffLL) return GMM_ERR_INVALID_ARGUMENT;
-  const long long cap = (long long)d.sm_count * 8;
-  const int grid = (int)(ub < cap ? ub : cap);
-  switch (p.in_dtype) {
-    case DT_BF16: return launch_generic_in<__nv_bfloat16>(p, grid, st);
-    case DT_F16: return launch_generic_in<__half>(p, grid, st);
-    default: return launch_generic_in<float>(p, grid, st);
-  }
+  // 128 x 128 tiles (64 outputs per thread) once there are enough of them to occupy every SM twice;
+  // 64 x 64 tiles otherwise, which waste less on short groups and spread a small problem wider.
+  const long long ub_large = tile_upper_bound(p, kGBML, kGBNL);
+  const bool tall = (p.mode == MODE_MRAGGED ? (long long)p.M / (p.G > 0 ? p.G : 1) : p.M) >= kGBML;
+  if (tall && p.N >= kGBNL && ub_large >= 2ll * d.sm_count)
+    return launch_generic_tile<kGBML, kGBNL>(p, ub_large, 1, d, st);  // 244 registers: one block per SM
+  return launch_generic_tile<kGBM, kGBN>(p, ub, 8, d, st);
 }
 
 template <bool KR>

@@ -16,8 +16,10 @@
 
 namespace gmm {
 
-constexpr int kGBM = 64;
+constexpr int kGBM = 64;    // small tile: few or short groups
 constexpr int kGBN = 64;
+constexpr int kGBML = 128;  // large tile: enough tiles of this size to fill the GPU
+constexpr int kGBNL = 128;
 constexpr int kGBK = 16;
 constexpr int kGenericThreads = 256;
 
@@ -39,85 +41,140 @@ __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { retu
 template <>
 __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
 
-template <typename TIn, typename TOut>
+// BM x BN output tile per block, 16 x 16 threads, (BM/16) x (BN/16) outputs per thread held as
+// 4 x 4 blocks spaced 64 apart (so that the shared-memory reads of a warp are conflict-free
+// float4 loads). The k-slab after the current one is fetched into registers while the current one
+// is multiplied, and parked in the second shared-memory buffer: one barrier per slab.
+template <typename TIn, typename TOut, int BM, int BN>
 __global__ void __launch_bounds__(kGenericThreads) gmm_generic_kernel(const CanonProblem p) {
+  static_assert(BM % 64 == 0 && BN % 64 == 0, "tiles are made of 64 x 64 quadrants");
+  constexpr int QM = BM / 64, QN = BN / 64;          // quadrants per tile
+  constexpr int EA = BM * kGBK / kGenericThreads;    // A elements a thread fetches per slab
+  constexpr int EB = BN * kGBK / kGenericThreads;
   __shared__ SchedSmem sched;
-  __shared__ float As[kGBK][kGBM + 4];
-  __shared__ float Bs[kGBK][kGBN + 4];
+  __shared__ __align__(16) float As[2][kGBK][BM + 4];  // two slabs: one multiplied while the next is filled
+  __shared__ __align__(16) float Bs[2][kGBK][BN + 4];
 
-  sched_init<kGBM, kGBN>(p, sched);
+  sched_init<BM, BN>(p, sched);
   const int total = sched.total;
   const int tid = threadIdx.x;
-  const int tx = tid & 15;  // 4 output columns each
-  const int ty = tid >> 4;  // 4 output rows each
+  const int tx = tid & 15;  // columns tx*4 .. tx*4+3 of every quadrant
+  const int ty = tid >> 4;  // rows    ty*4 .. ty*4+3 of every quadrant
 
   const TIn* a_all = reinterpret_cast<const TIn*>(p.a);
   const TIn* b_all = reinterpret_cast<const TIn*>(p.b);
   TOut* c_all = reinterpret_cast<TOut*>(p.c);
 
+  // Which element of a slab this thread fetches: walk the unit-stride dimension fastest for
+  // whichever layout the operand has.
+  int am[EA], ak[EA], bn[EB], bk[EB];
+#pragma unroll
+  for (int e = 0; e < EA; ++e) {
+    const int idx = tid + e * kGenericThreads;
+    if (p.a_sk == 1) { ak[e] = idx % kGBK; am[e] = idx / kGBK; } else { am[e] = idx % BM; ak[e] = idx / BM; }
+  }
+#pragma unroll
+  for (int e = 0; e < EB; ++e) {
+    const int idx = tid + e * kGenericThreads;
+    if (p.b_sn == 1) { bn[e] = idx % BN; bk[e] = idx / BN; } else { bk[e] = idx % kGBK; bn[e] = idx / kGBK; }
+  }
+
   for (int t = blockIdx.x; t < total; t += gridDim.x) {
-    const TileInfo ti = decode_tile<kGBM, kGBN>(p, sched, t);
-    const TIn* a_g = a_all + (long long)ti.g * p.a_sg;
-    const TIn* b_g = b_all + (long long)ti.g * p.b_sg;
-    const int ncols = min(kGBN, p.N - ti.n0);
+    const TileInfo ti = decode_tile<BM, BN>(p, sched, t);
+    const int ncols = min(BN, p.N - ti.n0);
+    // Element (row m, contraction index 0) of A and (0, column n) of B for this thread's fetches.
+    const TIn* a_src[EA];
+    const TIn* b_src[EB];
+#pragma unroll
+    for (int e = 0; e < EA; ++e)
+      a_src[e] = a_all + (long long)ti.g * p.a_sg + (long long)(ti.m0 + am[e]) * p.a_sm +
+                 (long long)(ti.k0 + ak[e]) * p.a_sk;
+#pragma unroll
+    for (int e = 0; e < EB; ++e)
+      b_src[e] = b_all + (long long)ti.g * p.b_sg + (long long)(ti.k0 + bk[e]) * p.b_sk +
+                 (long long)(ti.n0 + bn[e]) * p.b_sn;
 
-    float acc[4][4];
+    float acc[QM][QN][4][4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int qm = 0; qm < QM; ++qm)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
-
-    for (int kk = 0; kk < ti.klen; kk += kGBK) {
-      // A tile: kGBM x kGBK, B tile: kGBK x kGBN; 1024 elements each, 4 per thread.
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int idx = tid + e * kGenericThreads;
-        {
-          // Walk the unit-stride dimension fastest for whichever layout A has.
-          int m, k;
-          if (p.a_sk == 1) { k = idx % kGBK; m = idx / kGBK; } else { m = idx % kGBM; k = idx / kGBM; }
-          float v = 0.f;
-          if (m < ti.rows && kk + k < ti.klen)
-            v = to_f32<TIn>(a_g[(long long)(ti.m0 + m) * p.a_sm + (long long)(ti.k0 + kk + k) * p.a_sk]);
-          As[k][m] = v;
-        }
-        {
-          int n, k;
-          if (p.b_sn == 1) { n = idx % kGBN; k = idx / kGBN; } else { k = idx % kGBK; n = idx / kGBK; }
-          float v = 0.f;
-          if (n < ncols && kk + k < ti.klen)
-            v = to_f32<TIn>(b_g[(long long)(ti.k0 + kk + k) * p.b_sk + (long long)(ti.n0 + n) * p.b_sn]);
-          Bs[k][n] = v;
-        }
-      }
-      __syncthreads();
-#pragma unroll
-      for (int k = 0; k < kGBK; ++k) {
-        float av[4], bv[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) av[i] = As[k][ty * 4 + i];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) bv[j] = Bs[k][tx * 4 + j];
+      for (int qn = 0; qn < QN; ++qn)
 #pragma unroll
         for (int i = 0; i < 4; ++i)
 #pragma unroll
-          for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+          for (int j = 0; j < 4; ++j) acc[qm][qn][i][j] = 0.f;
+
+    float a_reg[EA], b_reg[EB];
+    auto fetch = [&](int kk) {
+#pragma unroll
+      for (int e = 0; e < EA; ++e) {
+        const bool ok = am[e] < ti.rows && kk + ak[e] < ti.klen;
+        a_reg[e] = ok ? to_f32<TIn>(a_src[e][(long long)kk * p.a_sk]) : 0.f;
       }
+#pragma unroll
+      for (int e = 0; e < EB; ++e) {
+        const bool ok = bn[e] < ncols && kk + bk[e] < ti.klen;
+        b_reg[e] = ok ? to_f32<TIn>(b_src[e][(long long)kk * p.b_sk]) : 0.f;
+      }
+    };
+
+    auto stash = [&](int buf) {
+#pragma unroll
+      for (int e = 0; e < EA; ++e) As[buf][ak[e]][am[e]] = a_reg[e];
+#pragma unroll
+      for (int e = 0; e < EB; ++e) Bs[buf][bk[e]][bn[e]] = b_reg[e];
+    };
+    int cur = 0;
+    if (ti.klen > 0) {
+      fetch(0);
+      stash(0);
+    }
+    __syncthreads();
+    for (int kk = 0; kk < ti.klen; kk += kGBK) {
+      const bool more = kk + kGBK < ti.klen;
+      if (more) fetch(kk + kGBK);  // in flight during the multiply below
+#pragma unroll
+      for (int k = 0; k < kGBK; ++k) {
+        float4 av[QM], bv[QN];
+#pragma unroll
+        for (int qm = 0; qm < QM; ++qm) av[qm] = *reinterpret_cast<const float4*>(&As[cur][k][qm * 64 + ty * 4]);
+#pragma unroll
+        for (int qn = 0; qn < QN; ++qn) bv[qn] = *reinterpret_cast<const float4*>(&Bs[cur][k][qn * 64 + tx * 4]);
+#pragma unroll
+        for (int qm = 0; qm < QM; ++qm) {
+          const float a4[4] = {av[qm].x, av[qm].y, av[qm].z, av[qm].w};
+#pragma unroll
+          for (int qn = 0; qn < QN; ++qn) {
+            const float b4[4] = {bv[qn].x, bv[qn].y, bv[qn].z, bv[qn].w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+              for (int j = 0; j < 4; ++j) acc[qm][qn][i][j] = fmaf(a4[i], b4[j], acc[qm][qn][i][j]);
+          }
+        }
+      }
+      if (more) stash(cur ^ 1);  // the other slab: nobody reads it during this iteration
       __syncthreads();
+      cur ^= 1;
     }
 
     TOut* c_g = c_all + (long long)ti.g * p.c_sg;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int m = ty * 4 + i;
-      if (m >= ti.rows) continue;
+    for (int qm = 0; qm < QM; ++qm)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int n = tx * 4 + j;
-        if (n < ncols)
-          c_g[(long long)(ti.m0 + m) * p.c_sm + (long long)(ti.n0 + n) * p.c_sn] = from_f32<TOut>(acc[i][j]);
+      for (int i = 0; i < 4; ++i) {
+        const int m = qm * 64 + ty * 4 + i;
+        if (m >= ti.rows) continue;
+#pragma unroll
+        for (int qn = 0; qn < QN; ++qn)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int n = qn * 64 + tx * 4 + j;
+            if (n < ncols)
+              c_g[(long long)(ti.m0 + m) * p.c_sm + (long long)(ti.n0 + n) * p.c_sn] =
+                  from_f32<TOut>(acc[qm][qn][i][j]);
+          }
       }
-    }
   }
 }
 
