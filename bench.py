@@ -341,7 +341,19 @@ def gated_up_leg(dev, experts: int = 8, hidden: int = 4096, inter: int = 14336):
     with torch.no_grad():
         fused_ms = time_steps(None, lambda: moe.gated_up_projection(x, w, offs), 20, 3) / 20
         two_ms = time_steps(None, two_step, 20, 3) / 20
+    # the whole routed block at the same shape: 16384 tokens, top-2
+    tokens, topk = sum(sizes) // 2, 2
+    ids = torch.randint(0, experts, (tokens, topk), device=dev, dtype=torch.int32, generator=gen)
+    xt = torch.randn((tokens, hidden), device=dev, generator=gen).bfloat16()
+    gates = torch.rand((tokens, topk), device=dev, generator=gen)
+    down = (torch.randn((experts, inter, hidden), device=dev, generator=gen) * 0.02).bfloat16()
+    with torch.no_grad():
+        layer_ms = time_steps(None, lambda: moe.feed_forward(xt, ids, gates, w, down), 20, 3) / 20
+    layer_flops = 2.0 * tokens * topk * hidden * 3 * inter
     return {"fused_ms": fused_ms, "fused_TFLOP/s": flops / (fused_ms * 1e-3) / 1e12, "two_step_ms": two_ms,
+            "feed_forward_block": {"ms": layer_ms, "tokens_per_s": tokens / (layer_ms * 1e-3),
+                                   "TFLOP/s": layer_flops / (layer_ms * 1e-3) / 1e12,
+                                   "what": f"moe.feed_forward: route, permute, gated up, down, combine; {tokens} tokens, top-{topk}"},
             "shape": f"{sum(sizes)} rows, {experts} experts, {hidden} -> 2 x {inter}, bf16",
             "what": "silu(x @ gate) * (x @ up): one kernel vs grouped_mm + torch silu * mul"}
 

@@ -4,7 +4,8 @@
 ``offs`` plus the row permutation; ``permute`` gathers token rows into group-contiguous order;
 ``combine`` sums each token's ``topk`` expert outputs back, weighted; ``gated_up_projection`` is the
 feed-forward block's first half, ``silu(x @ gate) * (x @ up)``, with the activation fused into the
-grouped GEMM's epilogue. The reference shows only the
+grouped GEMM's epilogue, and ``feed_forward`` chains all of them with the down-projection into
+one routed block. The reference shows only the
 offsets half of ``route``, on the host, in its benchmark (bench/bench_2d3d.py:131-138:
 ``bincount`` then ``cumsum``). Everything here runs in CUDA kernels of the same library, on the
 current stream, with no host synchronisation; there is no CPU path.
@@ -18,7 +19,7 @@ import torch
 
 from . import _lib, _op
 from ._op import _DTYPES
-from .api import forward_into, output_geometry
+from .api import forward_into, grouped_mm, output_geometry
 
 
 def _check(lib, rc: int) -> None:
@@ -186,3 +187,28 @@ def gated_up_projection(x: torch.Tensor, gate_up: torch.Tensor, offs: torch.Tens
     if out_dtype not in (x.dtype, torch.float32):
         raise RuntimeError("out_dtype must be the input dtype or float32")
     return _GatedUp.apply(x, gate_up, offs, out_dtype)
+
+
+def feed_forward(x: torch.Tensor, expert_ids: torch.Tensor, weights: Optional[torch.Tensor],
+                 gate_up: torch.Tensor, down: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """A routed gated feed-forward block, token rows in and token rows out:
+
+        out[t] = sum_k weights[t, k] * (silu(x[t] @ gate[e]) * (x[t] @ up[e])) @ down[e],   e = expert_ids[t, k]
+
+    ``x`` ``[tokens, hidden]``, ``expert_ids`` int32 ``[tokens, topk]``, ``weights`` ``[tokens, topk]``
+    (``None``: all ones), ``gate_up`` ``[experts, hidden, 2 * inter]`` (``[gate | up]``), ``down``
+    ``[experts, inter, hidden]``. Five launches on the current stream, none of which waits for the
+    host: ``route``, ``permute``, ``gated_up_projection``, ``grouped_mm`` and ``combine``. Assignments
+    whose expert id lies outside ``[0, experts)`` contribute nothing.
+    """
+    if expert_ids.dim() != 2 or expert_ids.size(0) != x.size(0):
+        raise RuntimeError("expert_ids has to be [tokens, topk]")
+    if gate_up.dim() != 3 or down.dim() != 3 or gate_up.size(0) != down.size(0) or \
+            gate_up.size(2) != 2 * down.size(1) or down.size(2) != x.size(1):
+        raise RuntimeError("expected gate_up [experts, hidden, 2 * inter] and down [experts, inter, hidden]")
+    topk, experts = expert_ids.size(1), gate_up.size(0)
+    offs, perm, inv = route(expert_ids, experts)
+    rows = permute(x, perm, topk)
+    hidden = gated_up_projection(rows, gate_up, offs)
+    y = grouped_mm(hidden, down, offs=offs)
+    return combine(y, inv, weights, topk, out_dtype=out_dtype)

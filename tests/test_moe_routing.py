@@ -111,3 +111,27 @@ def test_routed_layer_matches_dense_per_token_computation(built_library):
     per_choice = torch.einsum("tk,tckn->tcn", x.float(), wts.float()[ids.long()])  # [tokens, topk, n]
     ref = (per_choice.bfloat16().float() * gate.unsqueeze(-1)).sum(1)  # y is rounded to bf16 before the combine
     torch.testing.assert_close(out, ref, atol=2e-2, rtol=8e-3)
+
+
+@gpu
+def test_feed_forward_matches_dense_per_token_computation(built_library):
+    """moe.feed_forward equals, token by token, sum_k w_k * (silu(x @ gate_e) * (x @ up_e)) @ down_e."""
+    from grouped_mm_bf16_b200 import moe
+
+    tokens, topk, experts, hidden, inter = 384, 2, 8, 256, 320
+    ids = _ids(tokens, topk, experts, seed=9)
+    ids[7, 1] = experts + 3  # an assignment that is routed nowhere
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn(tokens, hidden, generator=g).bfloat16()
+    gate_up = (torch.randn(experts, hidden, 2 * inter, generator=g) * 0.06).bfloat16()
+    down = (torch.randn(experts, inter, hidden, generator=g) * 0.06).bfloat16()
+    w = torch.rand(tokens, topk, generator=g)
+    with torch.no_grad():
+        out = moe.feed_forward(x.cuda(), ids.cuda(), w.cuda(), gate_up.cuda(), down.cuda(), out_dtype=torch.float32).cpu()
+    valid = (ids >= 0) & (ids < experts)
+    e = ids.clamp(0, experts - 1).long()
+    both = torch.einsum("th,tchn->tcn", x.float(), gate_up.float()[e])             # [tokens, topk, 2 inter]
+    act = (torch.nn.functional.silu(both[..., :inter]) * both[..., inter:]).bfloat16().float()
+    y = torch.einsum("tci,tcih->tch", act, down.float()[e]).bfloat16().float()      # rounded like the kernels' outputs
+    ref = (y * (w * valid).unsqueeze(-1)).sum(1)
+    torch.testing.assert_close(out, ref, atol=2e-2, rtol=1e-2)
