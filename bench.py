@@ -358,6 +358,34 @@ def gated_up_leg(dev, experts: int = 8, hidden: int = 4096, inter: int = 14336):
             "what": "silu(x @ gate) * (x @ up): one kernel vs grouped_mm + torch silu * mul"}
 
 
+def expert_parallel_leg(dist, dev, rank: int, world: int, tokens: int = 16384, topk: int = 2, experts: int = 8,
+                        hidden: int = 4096, inter: int = 14336):
+    """Times the expert-parallel feed-forward block: every rank holds `tokens` tokens and experts / world
+    experts of the Mixtral shape; rows travel to their expert's rank and back by NCCL all-to-all."""
+    from grouped_mm_bf16_b200 import expert_parallel
+
+    if experts % world:
+        return {"unavailable": f"{experts} experts do not divide over {world} ranks"}
+    e_local = experts // world
+    gen = torch.Generator(device=dev).manual_seed(31 + rank)
+    x = torch.randn((tokens, hidden), device=dev, generator=gen).bfloat16()
+    ids = torch.randint(0, experts, (tokens, topk), device=dev, dtype=torch.int32, generator=gen)
+    gates = torch.rand((tokens, topk), device=dev, generator=gen)
+    gate_up = (torch.randn((e_local, hidden, 2 * inter), device=dev, generator=gen) * 0.02).bfloat16()
+    down = (torch.randn((e_local, inter, hidden), device=dev, generator=gen) * 0.02).bfloat16()
+
+    def step():
+        with torch.no_grad():
+            expert_parallel.feed_forward(x, ids, gates, gate_up, down)
+
+    steps = 10
+    ms = max_over_ranks(dist, time_steps(dist, step, steps, 3)) / steps
+    flops = 2.0 * tokens * world * topk * hidden * 3 * inter
+    return {"ms": ms, "tokens_per_s": tokens * world / (ms * 1e-3), "TFLOP/s": flops / (ms * 1e-3) / 1e12,
+            "what": f"expert_parallel.feed_forward: {tokens} tokens per rank, top-{topk} of {experts} experts "
+                    f"({e_local} per rank), {hidden} <-> {inter}; dispatch and combine by NCCL all-to-all"}
+
+
 # ----------------------------------------------------------------------------- main arm
 
 
@@ -375,6 +403,9 @@ def main():
                     help="shrink the ragged extent (routed rows) of the workload; for small profiling cases only")
     ap.add_argument("--no-baselines", action="store_true", help="skip the CPU and Triton baseline legs")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--ep-block", action="store_true",
+                    help="N > 1 only: also time the expert-parallel routed feed-forward block (NCCL all-to-all "
+                         "dispatch and combine around the grouped GEMMs); adds the key expert_parallel_block")
     ap.add_argument("--tf32", action="store_true",
                     help="fp32 operands multiplied as TF32 (torch.backends.cuda.matmul.allow_tf32 = True) instead of "
                          "the benchmark's bf16; a side measurement, reported against half the bf16 tensor peak")
@@ -492,6 +523,10 @@ def main():
                       "row_balance_mean_over_max": imbalance(sizes, world),
                       "note": "one 8-expert workload split by contiguous expert ranges, row-balanced"}
 
+    ep_block = None
+    if world > 1 and args.ep_block:
+        ep_block = expert_parallel_leg(dist, dev, rank, world)
+
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
@@ -510,6 +545,8 @@ def main():
             "roofline": roofline, "e2e": e2e, "gpu_launches": args.steps, "clocks": sampler.summary(),
             "device_status": status,
         }
+        if ep_block is not None:
+            line["expert_parallel_block"] = ep_block
         if strong is not None:
             line["strong_scaling"] = strong
         if world == 1 and not args.no_baselines:
