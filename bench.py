@@ -381,9 +381,26 @@ def expert_parallel_leg(dist, dev, rank: int, world: int, tokens: int = 16384, t
     steps = 10
     ms = max_over_ranks(dist, time_steps(dist, step, steps, 3)) / steps
     flops = 2.0 * tokens * world * topk * hidden * 3 * inter
-    return {"ms": ms, "tokens_per_s": tokens * world / (ms * 1e-3), "TFLOP/s": flops / (ms * 1e-3) / 1e12,
-            "what": f"expert_parallel.feed_forward: {tokens} tokens per rank, top-{topk} of {experts} experts "
-                    f"({e_local} per rank), {hidden} <-> {inter}; dispatch and combine by NCCL all-to-all"}
+    res = {"ms": ms, "tokens_per_s": tokens * world / (ms * 1e-3), "TFLOP/s": flops / (ms * 1e-3) / 1e12,
+           "what": f"expert_parallel.feed_forward: {tokens} tokens per rank, top-{topk} of {experts} experts "
+                   f"({e_local} per rank), {hidden} <-> {inter}; dispatch and combine by NCCL all-to-all"}
+    try:
+        buffers = expert_parallel.PeerBuffers(world * tokens * topk, hidden, torch.bfloat16, dev)
+
+        def peer_step():
+            with torch.no_grad():
+                expert_parallel.feed_forward_peer(x, ids, gates, gate_up, down, buffers)
+
+        p_ms = max_over_ranks(dist, time_steps(dist, peer_step, steps, 3)) / steps
+        from grouped_mm_bf16_b200 import _op
+
+        res["peer_memory"] = {"ms": p_ms, "tokens_per_s": tokens * world / (p_ms * 1e-3),
+                              "TFLOP/s": flops / (p_ms * 1e-3) / 1e12, "device_status": _op.check_status(dev),
+                              "what": "feed_forward_peer: rows stored into / loaded from the peers' buffers by this "
+                                      "package's kernels, no host synchronisation"}
+    except Exception as exc:
+        res["peer_memory"] = {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
+    return res
 
 
 # ----------------------------------------------------------------------------- main arm

@@ -23,6 +23,7 @@ GMM_FLAG_NO_PAIR = 0x4
 GMM_FLAG_ALLOW_TF32 = 0x8
 GMM_ERR_DEVICE_WAIT = -7
 GMM_ERR_NOT_FUSABLE = -8
+GMM_STATUS_BAD_PEER_INDEX = 0x40000000
 
 FORM_3D3D, FORM_2D3D, FORM_3D2D, FORM_2D2D = 0, 1, 2, 3
 
@@ -45,6 +46,8 @@ EXPORTED_SYMBOLS = (
     "gmm_route_build",
     "gmm_permute_rows",
     "gmm_combine_rows",
+    "gmm_scatter_rows_to_peers",
+    "gmm_combine_rows_from_peers",
 )
 
 
@@ -118,6 +121,11 @@ def load() -> ctypes.CDLL:
         lib.gmm_permute_rows.argtypes = [vp, i64, i64, i64, vp, i32, vp, i64, i64, vp]
         lib.gmm_combine_rows.restype = ctypes.c_int
         lib.gmm_combine_rows.argtypes = [vp, i32, i64, vp, vp, i32, i64, i32, vp, i32, i64, vp]
+        lib.gmm_scatter_rows_to_peers.restype = ctypes.c_int
+        lib.gmm_scatter_rows_to_peers.argtypes = [vp, i64, i64, i64, vp, i32, vp, vp, vp, i32, i64, i64, i64, vp, vp]
+        lib.gmm_combine_rows_from_peers.restype = ctypes.c_int
+        lib.gmm_combine_rows_from_peers.argtypes = [vp, i32, i32, i64, i64, vp, vp, vp, i32, i64, i32, vp, i32, i64,
+                                                    vp, vp]
         _lib = lib
         return lib
 

@@ -220,6 +220,35 @@ int gmm_combine_rows(const void* y, int32_t y_dtype, int64_t y_stride, const int
                      int32_t topk, int64_t n_tokens, int32_t n_cols, void* out, int32_t out_dtype, int64_t out_stride,
                      void* stream);
 
+/*
+ * Expert-parallel dispatch and combine over peer memory (no counterpart in the reference, which is
+ * single-GPU). `peers` is a DEVICE array of n_peers base pointers, entry i the buffer of rank i as
+ * mapped into this process (the caller sets the mapping up: CUDA IPC, fabric handles, symmetric
+ * memory), this rank's own buffer included; every buffer has capacity_rows rows. Rank and row of
+ * every transfer come from index tables in device memory; an index outside [0, n_peers) x
+ * [0, capacity_rows) is skipped and GMM_STATUS_BAD_PEER_INDEX is or-ed into *status (a device word).
+ * Neither call waits for the host or for another GPU: the caller puts a collective on the stream
+ * between "all ranks have scattered" and the first read of the received rows, and again between
+ * "all ranks have produced their results" and the combine.
+ *
+ * gmm_scatter_rows_to_peers: for r < n_rows with perm[r] >= 0 and dst_rank[r] >= 0,
+ *   row dst_row[r] of peers[dst_rank[r]]  =  src row perm[r] / topk      (strides in bytes)
+ * gmm_combine_rows_from_peers: out[t, :] = sum over k < topk of
+ *   weights[t*topk + k] * (row src_row[t*topk + k] of peers[src_rank[t*topk + k]]),
+ *   entries with src_rank < 0 skipped, fp32 accumulation (y_stride, out_stride in elements).
+ */
+#define GMM_STATUS_BAD_PEER_INDEX 0x40000000
+
+int gmm_scatter_rows_to_peers(const void* src, int64_t src_rows, int64_t row_bytes, int64_t src_stride_bytes,
+                              const int32_t* perm, int32_t topk, const int32_t* dst_rank, const int32_t* dst_row,
+                              void* const* peers, int32_t n_peers, int64_t dst_stride_bytes, int64_t capacity_rows,
+                              int64_t n_rows, int32_t* status, void* stream);
+
+int gmm_combine_rows_from_peers(const void* const* peers, int32_t n_peers, int32_t y_dtype, int64_t y_stride,
+                                int64_t capacity_rows, const int32_t* src_rank, const int32_t* src_row,
+                                const float* weights, int32_t topk, int64_t n_tokens, int32_t n_cols, void* out,
+                                int32_t out_dtype, int64_t out_stride, int32_t* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

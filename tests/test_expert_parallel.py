@@ -77,6 +77,51 @@ def test_received_rows_are_labelled_by_source_rank_then_expert():
     assert ep.split_sizes(counts, recv_counts) == ([2, 6], [3, 4])
 
 
+@pytest.mark.parametrize("world,e_local,topk", [(2, 4, 2), (3, 2, 3), (4, 1, 1)])
+def test_exchange_plan_places_every_row_once_in_expert_order(world, e_local, topk):
+    """All ranks simulated in one process: following every rank's tables, each routed row lands on
+    the owner of its expert, exactly once, inside that expert's segment of the owner's buffer, the
+    segments are what offs_local says, and the way back finds the same row again."""
+    experts = world * e_local
+    g = torch.Generator().manual_seed(world)
+    ids = [torch.randint(0, experts + 1, (20 + 7 * r, topk), generator=g, dtype=torch.int32) for r in range(world)]
+    routes = [route_oracle(i, experts) for i in ids]  # id == experts is routed nowhere
+    counts_all = torch.stack([torch.diff(o, prepend=o.new_zeros(1)) for o, _, _ in routes])
+    cap = int(counts_all.sum())
+    expert_at = [torch.full((cap,), -1, dtype=torch.long) for _ in range(world)]
+    origin_at = [torch.full((cap,), -1, dtype=torch.long) for _ in range(world)]
+    plans = []
+    for r in range(world):
+        offs, perm, inv = routes[r]
+        plan = ep.exchange_plan(offs, perm, inv, counts_all, r, e_local)
+        plans.append(plan)
+        dst_rank, dst_row = plan[0], plan[1]
+        assert all(t.dtype == torch.int32 for t in plan)
+        flat = ids[r].reshape(-1)
+        for p in range(perm.numel()):
+            if perm[p] < 0:
+                assert dst_rank[p] == -1 and dst_row[p] == -1
+                continue
+            assert expert_at[dst_rank[p]][dst_row[p]] == -1, "two rows were sent to the same place"
+            expert_at[dst_rank[p]][dst_row[p]] = int(flat[perm[p]])
+            origin_at[dst_rank[p]][dst_row[p]] = r * 10000 + int(perm[p])
+    for r in range(world):
+        offs_local = plans[r][4]
+        n = int(offs_local[-1])
+        assert bool((expert_at[r][:n] >= 0).all()) and bool((expert_at[r][n:] == -1).all())
+        start = 0
+        for e in range(e_local):
+            assert bool((expert_at[r][start:int(offs_local[e])] == r * e_local + e).all())
+            start = int(offs_local[e])
+        src_rank, src_row = plans[r][2], plans[r][3]
+        flat = ids[r].reshape(-1)
+        for a in range(flat.numel()):
+            if flat[a] >= experts:
+                assert src_rank[a] == -1
+            else:
+                assert origin_at[src_rank[a]][src_row[a]] == r * 10000 + a
+
+
 def _cpu_rank(rank: int, world: int, port: int, out_dir: str):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -100,8 +145,9 @@ def test_two_cpu_ranks_over_gloo_match_the_dense_computation(tmp_path):
         assert res["err"] <= 1e-4 * max(1.0, res["scale"]), res
 
 
-def _gpu_rank(rank: int, world: int, port: int, out_dir: str):
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+def _gpu_rank(rank: int, world: int, port: int, out_dir: str, peer_memory: bool = False):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
+                      TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
@@ -111,9 +157,15 @@ def _gpu_rank(rank: int, world: int, port: int, out_dir: str):
         x, ids, w, gate_up, down = _problem(rank, torch.bfloat16)
         e_local = EXPERTS // world
         mine = slice(rank * e_local, (rank + 1) * e_local)
+        args = (x.to(dev), ids.to(dev), w.to(dev), gate_up[mine].to(dev), down[mine].to(dev))
         with torch.no_grad():
-            out = ep.feed_forward(x.to(dev), ids.to(dev), w.to(dev), gate_up[mine].to(dev), down[mine].to(dev),
-                                  out_dtype=torch.float32)
+            if peer_memory:
+                buffers = ep.PeerBuffers(world * 64 * TOPK, HIDDEN, torch.bfloat16, dev)
+                out = ep.feed_forward_peer(*args, buffers, out_dtype=torch.float32)
+                out2 = ep.feed_forward_peer(*args, buffers, out_dtype=torch.float32)  # buffers are reusable
+                assert torch.equal(out, out2)
+            else:
+                out = ep.feed_forward(*args, out_dtype=torch.float32)
         status = _op.check_status(dev)
         ref = _dense_reference(x, ids, w, gate_up, down, round_to=torch.bfloat16)
         torch.save(dict(out=out.cpu(), ref=ref, status=status), os.path.join(out_dir, f"rank{rank}.pt"))
@@ -126,6 +178,18 @@ def test_two_gpus_over_nccl_match_the_dense_computation(tmp_path, built_library)
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     mp.spawn(_gpu_rank, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    for rank in (0, 1):
+        res = torch.load(tmp_path / f"rank{rank}.pt")
+        assert res["status"] == 0
+        torch.testing.assert_close(res["out"], res["ref"], atol=2e-2, rtol=1e-2)
+
+
+@pytest.mark.gpu
+def test_two_gpus_with_rows_moved_over_peer_memory(tmp_path, built_library):
+    """The same block with the dispatch written into, and the combine read from, the peers' buffers."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    mp.spawn(_gpu_rank, args=(2, _free_port(), str(tmp_path), True), nprocs=2, join=True)
     for rank in (0, 1):
         res = torch.load(tmp_path / f"rank{rank}.pt")
         assert res["status"] == 0
