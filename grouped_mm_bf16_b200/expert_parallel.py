@@ -19,6 +19,10 @@ The GEMM kernels only ever read this GPU's memory: received rows land in a local
 The local steps are taken from an ``ops`` namespace so that the index arithmetic and the exchange
 can be checked on CPU ranks over gloo with host stand-ins for the kernels; the default is the CUDA
 implementation, and there is no CPU fallback inside it.
+
+``feed_forward_peer`` (second half of this file) is the same block without the all-to-alls and
+without the host synchronisation: the rows are stored into, and the results loaded from, the
+peers' buffers by this package's own kernels.
 """
 
 from __future__ import annotations
