@@ -135,3 +135,38 @@ def test_feed_forward_matches_dense_per_token_computation(built_library):
     y = torch.einsum("tci,tcih->tch", act, down.float()[e]).bfloat16().float()      # rounded like the kernels' outputs
     ref = (y * (w * valid).unsqueeze(-1)).sum(1)
     torch.testing.assert_close(out, ref, atol=2e-2, rtol=1e-2)
+
+
+@gpu
+def test_feed_forward_replays_from_a_cuda_graph(built_library):
+    """No step of the block needs the host, so the whole block can be captured once and replayed on
+    new tokens and new routing written into the same buffers."""
+    from grouped_mm_bf16_b200 import moe
+
+    tokens, topk, experts, hidden, inter = 256, 2, 8, 128, 192
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(21)
+    gate_up = (torch.randn((experts, hidden, 2 * inter), device=dev, generator=g) * 0.08).bfloat16()
+    down = (torch.randn((experts, inter, hidden), device=dev, generator=g) * 0.08).bfloat16()
+    x = torch.randn((tokens, hidden), device=dev, generator=g).bfloat16()
+    ids = torch.randint(0, experts, (tokens, topk), device=dev, dtype=torch.int32, generator=g)
+    w = torch.rand((tokens, topk), device=dev, generator=g)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side), torch.no_grad():
+        for _ in range(2):  # warm-up outside the capture: library load, workspace, allocator pools
+            moe.feed_forward(x, ids, w, gate_up, down)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph), torch.no_grad():
+        out = moe.feed_forward(x, ids, w, gate_up, down)
+    for seed in (22, 23):
+        g2 = torch.Generator(device=dev).manual_seed(seed)
+        x.copy_(torch.randn((tokens, hidden), device=dev, generator=g2).bfloat16())
+        ids.copy_(torch.randint(0, experts, (tokens, topk), device=dev, dtype=torch.int32, generator=g2))
+        w.copy_(torch.rand((tokens, topk), device=dev, generator=g2))
+        graph.replay()
+        with torch.no_grad():
+            eager = moe.feed_forward(x, ids, w, gate_up, down)
+        torch.cuda.synchronize()
+        assert torch.equal(out, eager)
