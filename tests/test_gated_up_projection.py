@@ -84,7 +84,8 @@ SIZES = [
 @gpu
 @pytest.mark.parametrize("pair", [False, True])
 @pytest.mark.parametrize("sizes", SIZES)
-@pytest.mark.parametrize("k,n,col_major", [(64, 48, False), (200, 136, False), (72, 264, True), (8, 8, True), (64, 128, False)])
+@pytest.mark.parametrize("k,n,col_major", [(64, 48, False), (200, 136, False), (72, 264, True), (8, 8, True), (64, 128, False),
+                                          (72, 36, True), (64, 21, True)])  # column-major weights: any N
 def test_fused_matches_oracle(sizes, k, n, col_major, pair, monkeypatch, _clear_status):
     g = torch.Generator(device=DEV).manual_seed(len(sizes) * 100 + k + n)
     x = (torch.randn((sum(sizes), k), device=DEV, generator=g) * 0.5).bfloat16()
