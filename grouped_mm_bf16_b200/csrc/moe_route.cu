@@ -141,7 +141,16 @@ permute_rows_kernel(const unsigned char* src, long long src_stride, const int32_
   if (a < 0 || t >= src_rows) return;
   const V* s = reinterpret_cast<const V*>(src + t * src_stride);
   V* d = reinterpret_cast<V*>(dst + r * dst_stride);
-  for (int i = threadIdx.x; i < n_vec; i += blockDim.x) d[i] = s[i];
+  // four loads in flight per thread before the first store
+  int i = threadIdx.x;
+  for (; i + 3 * (int)blockDim.x < n_vec; i += 4 * blockDim.x) {
+    const V v0 = s[i], v1 = s[i + blockDim.x], v2 = s[i + 2 * blockDim.x], v3 = s[i + 3 * blockDim.x];
+    d[i] = v0;
+    d[i + blockDim.x] = v1;
+    d[i + 2 * blockDim.x] = v2;
+    d[i + 3 * blockDim.x] = v3;
+  }
+  for (; i < n_vec; i += blockDim.x) d[i] = s[i];
 }
 
 template <typename T>
