@@ -59,14 +59,20 @@ struct FastSmemTail {
 };
 
 // Per-warp staging area used to turn "one thread = one output row" (the TMEM read layout) into
-// row-contiguous global stores: 32 rows of 128 bytes, padded to 144 so that both the row-wise
-// writes and the transposed reads are free of bank conflicts.
-constexpr int kStageRowBytes = 144;
+// row-contiguous global stores: 32 rows of 128 bytes, the 16-byte segments of row r stored at
+// position (segment ^ (r & 7)). That is the 128-byte swizzle of the tensor maps, so a TMA store can
+// read the area as a 32-row box, and it keeps both the row-wise writes and the transposed reads
+// free of bank conflicts. Each warp's area starts on a 1024-byte boundary.
+constexpr int kStageRowBytes = 128;
 constexpr int kWarpStageBytes = 32 * kStageRowBytes;
 constexpr int kEpilogueStageBytes = 4 * kWarpStageBytes;
 
+__device__ __forceinline__ uint4* stage_seg(uint8_t* stage, int row, int seg) {
+  return reinterpret_cast<uint4*>(stage + row * kStageRowBytes + ((seg ^ (row & 7)) << 4));
+}
+
 constexpr size_t kFastSmemBytes =
-    1024 /*alignment slack*/ + size_t(kStages) * kStageBytes + sizeof(FastSmemTail) + kEpilogueStageBytes;
+    1024 /*alignment slack*/ + size_t(kStages) * kStageBytes + kEpilogueStageBytes + sizeof(FastSmemTail);
 
 struct FastParams {
   CanonProblem p;
@@ -169,7 +175,6 @@ __device__ __forceinline__ void epilogue_store_warp(uint32_t t_row, TOut* c_warp
       for (int i = 0; i < CW; ++i) r[i] = 0;
     }
     if (rows_aligned && c0 + CW <= ncols) {
-      uint4* mine = reinterpret_cast<uint4*>(stage + lane * kStageRowBytes);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         uint4 v;
@@ -181,7 +186,7 @@ __device__ __forceinline__ void epilogue_store_warp(uint32_t t_row, TOut* c_warp
           v.z = OutCvt<TOut>::pack2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
           v.w = OutCvt<TOut>::pack2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
         }
-        mine[j] = v;
+        *stage_seg(stage, lane, j) = v;
       }
       __syncwarp();
       const int seg = lane & 7;   // 16-byte segment of the 128-byte row chunk
@@ -189,7 +194,7 @@ __device__ __forceinline__ void epilogue_store_warp(uint32_t t_row, TOut* c_warp
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int row = i * 4 + sub;
-        const uint4 v = *reinterpret_cast<const uint4*>(stage + row * kStageRowBytes + seg * 16);
+        const uint4 v = *stage_seg(stage, row, seg);
         if (row < rows) {
           uint8_t* dst = reinterpret_cast<uint8_t*>(c_warp + (long long)row * c_sm + c0) + seg * 16;
           *reinterpret_cast<uint4*>(dst) = v;
@@ -238,10 +243,10 @@ __device__ __forceinline__ void epilogue_store_warp_swiglu(uint32_t t_row, TOut*
 #pragma unroll
       for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(silu_mul(__uint_as_float(v[i]), __uint_as_float(up[i])));
       if (whole) {
-        uint4* mine = reinterpret_cast<uint4*>(stage + lane * kStageRowBytes + h * 32 * (int)sizeof(TOut));
         if constexpr (sizeof(TOut) == 4) {
 #pragma unroll
-          for (int j = 0; j < 8; ++j) mine[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          for (int j = 0; j < 8; ++j)
+            *stage_seg(stage, lane, j) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
         } else {
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
@@ -250,7 +255,7 @@ __device__ __forceinline__ void epilogue_store_warp_swiglu(uint32_t t_row, TOut*
             w.y = OutCvt<TOut>::pack2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
             w.z = OutCvt<TOut>::pack2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
             w.w = OutCvt<TOut>::pack2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
-            mine[j] = w;
+            *stage_seg(stage, lane, h * 4 + j) = w;
           }
         }
       } else if (row_ok) {
@@ -264,7 +269,7 @@ __device__ __forceinline__ void epilogue_store_warp_swiglu(uint32_t t_row, TOut*
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int row = i * 4 + sub;
-        const uint4 w = *reinterpret_cast<const uint4*>(stage + row * kStageRowBytes + seg * 16);
+        const uint4 w = *stage_seg(stage, row, seg);
         if (row < rows) {
           uint8_t* dst = reinterpret_cast<uint8_t*>(c_warp + (long long)row * c_sm + c0) + seg * 16;
           *reinterpret_cast<uint4*>(dst) = w;
@@ -286,8 +291,8 @@ gmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* smem_a = smem;
   uint8_t* smem_b = smem + kStages * kAStageBytes;
-  FastSmemTail& tail = *reinterpret_cast<FastSmemTail*>(smem + kStages * kStageBytes);
-  uint8_t* epi_stage = smem + kStages * kStageBytes + ((sizeof(FastSmemTail) + 15) & ~size_t(15));
+  uint8_t* epi_stage = smem + kStages * kStageBytes;  // 1024-byte aligned, like the stages before it
+  FastSmemTail& tail = *reinterpret_cast<FastSmemTail*>(epi_stage + kEpilogueStageBytes);
   volatile int* abort_flag = &tail.abort_flag;
 
   using EG = ElemGeom<ES>;

@@ -45,7 +45,7 @@ struct PairSmemTail {
 };
 
 constexpr size_t kPairSmemBytes =
-    1024 + size_t(kPairStages) * kPairStageBytes + sizeof(PairSmemTail) + kEpilogueStageBytes;
+    1024 + size_t(kPairStages) * kPairStageBytes + kEpilogueStageBytes + sizeof(PairSmemTail);
 
 enum PairStatus : int {
   ST_PAIR_PRODUCER_TIMEOUT = 0x201,
@@ -80,8 +80,8 @@ gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* smem_a = smem;
   uint8_t* smem_b = smem + kPairStages * kPairAStageBytes;
-  PairSmemTail& tail = *reinterpret_cast<PairSmemTail*>(smem + kPairStages * kPairStageBytes);
-  uint8_t* epi_stage = smem + kPairStages * kPairStageBytes + ((sizeof(PairSmemTail) + 15) & ~size_t(15));
+  uint8_t* epi_stage = smem + kPairStages * kPairStageBytes;  // 1024-byte aligned
+  PairSmemTail& tail = *reinterpret_cast<PairSmemTail*>(epi_stage + kEpilogueStageBytes);
   volatile int* abort_flag = &tail.abort_flag;
 
   using EG = ElemGeom<ES>;
