@@ -356,16 +356,17 @@ int launch_generic(const CanonProblem& p, const DeviceInfo& d, cudaStream_t st) 
 }
 
 template <bool KR>
-int launch_fast_kr(const CUtensorMap& ta, const CUtensorMap& tb, const FastParams& fp, int grid, cudaStream_t st) {
+int launch_fast_kr(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const FastParams& fp, int grid,
+                   cudaStream_t st) {
   switch (fp.p.out_dtype) {
     case DT_BF16:
-      gmm_sm100_kernel<KR, __nv_bfloat16><<<grid, kFastThreads, kFastSmemBytes, st>>>(ta, tb, fp);
+      gmm_sm100_kernel<KR, __nv_bfloat16><<<grid, kFastThreads, kFastSmemBytes, st>>>(ta, tb, tc, fp);
       break;
     case DT_F16:
-      gmm_sm100_kernel<KR, __half><<<grid, kFastThreads, kFastSmemBytes, st>>>(ta, tb, fp);
+      gmm_sm100_kernel<KR, __half><<<grid, kFastThreads, kFastSmemBytes, st>>>(ta, tb, tc, fp);
       break;
     default:
-      gmm_sm100_kernel<KR, float><<<grid, kFastThreads, kFastSmemBytes, st>>>(ta, tb, fp);
+      gmm_sm100_kernel<KR, float><<<grid, kFastThreads, kFastSmemBytes, st>>>(ta, tb, tc, fp);
       break;
   }
   GMM_CUDA_TRY(cudaGetLastError());
@@ -373,11 +374,12 @@ int launch_fast_kr(const CUtensorMap& ta, const CUtensorMap& tb, const FastParam
 }
 
 template <typename TOut>
-int launch_pair_t(const CUtensorMap& ta, const CUtensorMap& tb, const FastParams& fp, int grid, cudaStream_t st) {
+int launch_pair_t(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const FastParams& fp, int grid,
+                  cudaStream_t st) {
   if (fp.p.mode == MODE_KRAGGED)
-    gmm_sm100_pair_kernel<true, TOut><<<grid, kFastThreads, kPairSmemBytes, st>>>(ta, tb, fp);
+    gmm_sm100_pair_kernel<true, TOut><<<grid, kFastThreads, kPairSmemBytes, st>>>(ta, tb, tc, fp);
   else
-    gmm_sm100_pair_kernel<false, TOut><<<grid, kFastThreads, kPairSmemBytes, st>>>(ta, tb, fp);
+    gmm_sm100_pair_kernel<false, TOut><<<grid, kFastThreads, kPairSmemBytes, st>>>(ta, tb, tc, fp);
   GMM_CUDA_TRY(cudaGetLastError());
   return GMM_OK;
 }
@@ -395,12 +397,12 @@ int choose_panel(const CanonProblem& p) {
 }
 
 template <typename TOut>
-int launch_swiglu_t(const CUtensorMap& ta, const CUtensorMap& tb, const FastParams& fp, bool pair, int grid,
-                    cudaStream_t st) {
+int launch_swiglu_t(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const FastParams& fp, bool pair,
+                    int grid, cudaStream_t st) {
   if (pair)
-    gmm_sm100_pair_kernel<false, TOut, true><<<grid, kFastThreads, kPairSmemBytes, st>>>(ta, tb, fp);
+    gmm_sm100_pair_kernel<false, TOut, true><<<grid, kFastThreads, kPairSmemBytes, st>>>(ta, tb, tc, fp);
   else
-    gmm_sm100_kernel<false, TOut, 2, true><<<grid, kFastThreads, kFastSmemBytes, st>>>(ta, tb, fp);
+    gmm_sm100_kernel<false, TOut, 2, true><<<grid, kFastThreads, kFastSmemBytes, st>>>(ta, tb, tc, fp);
   GMM_CUDA_TRY(cudaGetLastError());
   return GMM_OK;
 }
@@ -435,41 +437,55 @@ int launch_fast(const CanonProblem& p_in, const FastPlan& plan, const DeviceInfo
     rc = encode_map(&tb, p.b, p.in_dtype, true, b_cols, p.K, b_batched ? p.G : 1, p.b_sk, p.b_sg, bk);
   if (rc != GMM_OK) return rc;
 
+  // Output map for TMA stores of whole 32-row x 128-byte pieces: needs a unit column stride and
+  // 16-byte aligned rows (the operator's own outputs have both; a caller's strided view may not).
+  CUtensorMap tc = {};
+  const long long c_es = (p.out_dtype == DT_F32) ? 4 : 2;
+  const bool c_batched = (p.mode != MODE_MRAGGED);
+  bool c_tma = !swiglu && p.c_sn == 1 && aligned16(p.c) && (p.c_sm * c_es) % 16 == 0 && p.c_sm >= p.N &&
+               (!c_batched || p.G <= 1 || (p.c_sg > 0 && (p.c_sg * c_es) % 16 == 0)) &&
+               env_int("GROUPED_MM_B200_TMA_STORE", 1) != 0;
+  if (c_tma) {
+    rc = encode_map(&tc, p.c, p.out_dtype, false, p.N, p.M, c_batched ? p.G : 1, p.c_sm, p.c_sg, 32);
+    if (rc != GMM_OK) return rc;
+  }
+
   FastParams fp;
   fp.p = p;
   fp.a_mn = plan.a_mn;
   fp.b_mn = plan.b_mn;
+  fp.c_tma = c_tma ? 1 : 0;
   fp.idesc = make_idesc(p.in_dtype, plan.a_mn, plan.b_mn, plan.pair ? 256 : 128);
   if (swiglu) {
     switch (p.out_dtype) {
-      case DT_BF16: return launch_swiglu_t<__nv_bfloat16>(ta, tb, fp, plan.pair, grid, st);
-      case DT_F16: return launch_swiglu_t<__half>(ta, tb, fp, plan.pair, grid, st);
-      default: return launch_swiglu_t<float>(ta, tb, fp, plan.pair, grid, st);
+      case DT_BF16: return launch_swiglu_t<__nv_bfloat16>(ta, tb, tc, fp, plan.pair, grid, st);
+      case DT_F16: return launch_swiglu_t<__half>(ta, tb, tc, fp, plan.pair, grid, st);
+      default: return launch_swiglu_t<float>(ta, tb, tc, fp, plan.pair, grid, st);
     }
   }
   if (tf32) {
     if (plan.pair) {
       if (p.mode == MODE_KRAGGED)
-        gmm_sm100_pair_kernel<true, float, false, 4><<<grid, kFastThreads, kPairSmemBytes, st>>>(ta, tb, fp);
+        gmm_sm100_pair_kernel<true, float, false, 4><<<grid, kFastThreads, kPairSmemBytes, st>>>(ta, tb, tc, fp);
       else
-        gmm_sm100_pair_kernel<false, float, false, 4><<<grid, kFastThreads, kPairSmemBytes, st>>>(ta, tb, fp);
+        gmm_sm100_pair_kernel<false, float, false, 4><<<grid, kFastThreads, kPairSmemBytes, st>>>(ta, tb, tc, fp);
     } else if (p.mode == MODE_KRAGGED) {
-      gmm_sm100_kernel<true, float, 4><<<grid, kFastThreads, kFastSmemBytes, st>>>(ta, tb, fp);
+      gmm_sm100_kernel<true, float, 4><<<grid, kFastThreads, kFastSmemBytes, st>>>(ta, tb, tc, fp);
     } else {
-      gmm_sm100_kernel<false, float, 4><<<grid, kFastThreads, kFastSmemBytes, st>>>(ta, tb, fp);
+      gmm_sm100_kernel<false, float, 4><<<grid, kFastThreads, kFastSmemBytes, st>>>(ta, tb, tc, fp);
     }
     GMM_CUDA_TRY(cudaGetLastError());
     return GMM_OK;
   }
   if (plan.pair) {
     switch (p.out_dtype) {
-      case DT_BF16: return launch_pair_t<__nv_bfloat16>(ta, tb, fp, grid, st);
-      case DT_F16: return launch_pair_t<__half>(ta, tb, fp, grid, st);
-      default: return launch_pair_t<float>(ta, tb, fp, grid, st);
+      case DT_BF16: return launch_pair_t<__nv_bfloat16>(ta, tb, tc, fp, grid, st);
+      case DT_F16: return launch_pair_t<__half>(ta, tb, tc, fp, grid, st);
+      default: return launch_pair_t<float>(ta, tb, tc, fp, grid, st);
     }
   }
-  return p.mode == MODE_KRAGGED ? launch_fast_kr<true>(ta, tb, fp, grid, st)
-                                : launch_fast_kr<false>(ta, tb, fp, grid, st);
+  return p.mode == MODE_KRAGGED ? launch_fast_kr<true>(ta, tb, tc, fp, grid, st)
+                                : launch_fast_kr<false>(ta, tb, tc, fp, grid, st);
 }
 
 constexpr size_t kWorkspaceBytes = 256;

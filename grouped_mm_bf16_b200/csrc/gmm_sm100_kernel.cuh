@@ -79,6 +79,8 @@ struct FastParams {
   uint32_t idesc;  // tcgen05 instruction descriptor (formats, majors, M=128, N=256)
   int a_mn;        // 1: A is MN-major in memory (column-major [M,K]); 0: K-major
   int b_mn;        // 1: B is MN-major in memory (row-major [K,N]);    0: K-major
+  int c_tma;       // 1: the output has a tensor map (unit column stride, 16-byte aligned rows): whole
+                   //    32-row x 128-byte pieces of a tile are written with TMA stores
 };
 
 // Status codes written to CanonProblem::status when a bounded wait gives up.
@@ -149,11 +151,17 @@ __device__ __forceinline__ void store_row_chunk(TOut* dst, long long col_stride,
 //
 // Fast path (unit column stride, 16-byte aligned rows, full 128-byte chunk): each thread converts
 // 128 bytes of its row and parks them in shared memory; the warp then writes 4 rows x 128 bytes per
-// instruction, i.e. whole cache lines, instead of 32 scattered 16-byte pieces.
+// instruction, i.e. whole cache lines, instead of 32 scattered 16-byte pieces. When the output has a
+// tensor map (`tmap_c`, else null) and all 32 rows are valid, one TMA store of the 32 x 128-byte
+// box replaces those loads and stores; (cx, cy, cz) are the box coordinates of the warp's first
+// row at column 0 of the tile.
 template <typename TOut>
 __device__ __forceinline__ void epilogue_store_warp(uint32_t t_row, TOut* c_warp, long long c_sm, long long c_sn,
-                                                    int rows, int ncols, uint8_t* stage, bool zero_tile, int lane) {
+                                                    int rows, int ncols, uint8_t* stage, bool zero_tile, int lane,
+                                                    const CUtensorMap* tmap_c = nullptr, int cx = 0, int cy = 0,
+                                                    int cz = 0) {
   constexpr int CW = 128 / (int)sizeof(TOut);  // columns per 128-byte chunk: 32 (fp32) or 64 (16-bit)
+  const bool by_tma = tmap_c != nullptr && rows >= 32;
   const bool rows_aligned = (c_sn == 1) && ((reinterpret_cast<uintptr_t>(c_warp) & 15u) == 0) &&
                             (((c_sm * (long long)sizeof(TOut)) & 15) == 0);
   const bool row_ok = lane < rows;
@@ -175,6 +183,12 @@ __device__ __forceinline__ void epilogue_store_warp(uint32_t t_row, TOut* c_warp
       for (int i = 0; i < CW; ++i) r[i] = 0;
     }
     if (rows_aligned && c0 + CW <= ncols) {
+      if (tmap_c != nullptr) {
+        // A TMA store issued for the previous chunk, or for the previous tile, may still be reading
+        // the staging area (lane 0 issues them all, so its wait covers them all).
+        if (lane == 0) tma_store_wait_read();
+        __syncwarp();
+      }
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         uint4 v;
@@ -187,6 +201,15 @@ __device__ __forceinline__ void epilogue_store_warp(uint32_t t_row, TOut* c_warp
           v.w = OutCvt<TOut>::pack2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
         }
         *stage_seg(stage, lane, j) = v;
+      }
+      if (by_tma) {
+        fence_proxy_async_smem();  // this thread's row is visible to the TMA engine
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_3d(tmap_c, stage, cx + c0, cy, cz);
+          tma_store_commit();
+        }
+        continue;
       }
       __syncwarp();
       const int seg = lane & 7;   // 16-byte segment of the 128-byte row chunk
@@ -285,7 +308,7 @@ __device__ __forceinline__ void epilogue_store_warp_swiglu(uint32_t t_row, TOut*
 template <bool KRAGGED, typename TOut, int ES = 2, bool SWIGLU = false>
 __global__ void __launch_bounds__(kFastThreads, 1)
 gmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 const FastParams fp) {
+                 const __grid_constant__ CUtensorMap tmap_c, const FastParams fp) {
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzled tiles must start on 1024-byte boundaries.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -507,10 +530,13 @@ gmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                                          epi_stage + (warp - 2) * kWarpStageBytes, lane);
       else
         epilogue_store_warp<TOut>(t_row, c_warp, p.c_sm, p.c_sn, ti.rows - q * 32, ncols_tile,
-                                  epi_stage + (warp - 2) * kWarpStageBytes, zero_tile, lane);
+                                  epi_stage + (warp - 2) * kWarpStageBytes, zero_tile, lane,
+                                  fp.c_tma ? &tmap_c : nullptr, ti.n0, ti.m0 + q * 32,
+                                  p.mode == MODE_MRAGGED ? 0 : ti.g);
       tcgen05_fence_before_sync();
       mbar_arrive(&tail.acc_empty[buf]);
     }
+    if (fp.c_tma && lane == 0) tma_store_wait_all();  // the staging area outlives its last store
   }
 
   // ------------------------------------------------------------ teardown

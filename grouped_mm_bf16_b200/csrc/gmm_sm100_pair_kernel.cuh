@@ -75,7 +75,7 @@ __device__ __forceinline__ void zero_tail_rows(uint8_t* stage_buf, int r, int la
 template <bool KRAGGED, typename TOut, bool SWIGLU = false, int ES = 2>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFastThreads, 1)
 gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                      const FastParams fp) {
+                      const __grid_constant__ CUtensorMap tmap_c, const FastParams fp) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* smem_a = smem;
@@ -308,11 +308,14 @@ gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                                            epi_stage + (warp - 2) * kWarpStageBytes, lane);
         else
           epilogue_store_warp<TOut>(t_row, c_warp, p.c_sm, p.c_sn, ti.rows - row0, ncols_tile,
-                                    epi_stage + (warp - 2) * kWarpStageBytes, KRAGGED && ti.klen == 0, lane);
+                                    epi_stage + (warp - 2) * kWarpStageBytes, KRAGGED && ti.klen == 0, lane,
+                                    fp.c_tma ? &tmap_c : nullptr, ti.n0, ti.m0 + row0,
+                                    p.mode == MODE_MRAGGED ? 0 : ti.g);
       }
       tcgen05_fence_before_sync();
       mbar_arrive_cluster(map_to_cta(smem_u32(&tail.acc_empty[buf]), 0));
     }
+    if (fp.c_tma && lane == 0) tma_store_wait_all();  // the staging area outlives its last store
   }
 
   // ------------------------------------------------------------ teardown
