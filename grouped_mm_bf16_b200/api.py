@@ -174,6 +174,64 @@ def _stride_valid(t: torch.Tensor) -> torch.Tensor:
         return t.contiguous()
 
 
+def _grad_operand(grad_out: torch.Tensor, like: torch.Tensor) -> torch.Tensor:
+    """``grad_out`` in a layout and dtype the forward kernels take as an operand."""
+    g = _stride_valid(grad_out)
+    return g if g.dtype == like.dtype else g.to(like.dtype)
+
+
+# Kernel-level backward functions with the reference's names and signatures
+# (grouped_mm_bf16/kernels.py:1093, 1155, 1264, 1332): ``grad_a`` / ``grad_b`` are pre-allocated (or
+# None when not needed) and fully written, zeros included. Each gradient is one forward call on
+# transposed views, so the reference's fp32 scratch buffers and atomics (kernels.py:1232, 1303, 986)
+# have no counterpart.
+
+
+def grouped_mm_3d3d_backward(mat_a, mat_b, grad_out, grad_a, grad_b) -> None:
+    """C[g] = A[g] B[g]:  dA[g] = dC[g] B[g]^T,  dB[g] = A[g]^T dC[g]."""
+    g = _grad_operand(grad_out, mat_a)
+    if grad_a is not None:
+        forward_into(g, mat_b.transpose(-2, -1), None, grad_a)
+    if grad_b is not None:
+        forward_into(mat_a.transpose(-2, -1), g, None, grad_b)
+
+
+def grouped_mm_2d3d_backward(mat_a, mat_b, offs, grad_out, grad_a, grad_b) -> None:
+    """C[rows_g] = A[rows_g] B[g]:  dA[rows_g] = dC[rows_g] B[g]^T (2D x 3D), dB[g] = A[rows_g]^T dC[rows_g]
+    (2D x 2D; empty groups give zeros). Rows past offs[-1] belong to no group: their gradient is zero."""
+    g = _grad_operand(grad_out, mat_a)
+    if grad_a is not None:
+        grad_a.zero_()
+        forward_into(g, mat_b.transpose(-2, -1), offs, grad_a)
+    if grad_b is not None:
+        forward_into(mat_a.transpose(-2, -1), g, offs, grad_b)
+
+
+def grouped_mm_2d2d_backward(mat_a, mat_b, offs, grad_out, grad_a, grad_b) -> None:
+    """C[g] = A[:,ks:ke] B[ks:ke,:]:  dA[:,ks:ke] = dC[g] B[ks:ke,:]^T (3D x 2D),
+    dB[ks:ke,:] = A[:,ks:ke]^T dC[g] (2D x 3D). Indices past offs[-1] get zero gradient."""
+    g = _grad_operand(grad_out, mat_a)
+    if grad_a is not None:
+        grad_a.zero_()
+        forward_into(g, mat_b.transpose(-2, -1), offs, grad_a)
+    if grad_b is not None:
+        grad_b.zero_()
+        forward_into(mat_a.transpose(-2, -1), g, offs, grad_b)
+
+
+def grouped_mm_3d2d_backward(mat_a, mat_b, offs, grad_out, grad_a, grad_b) -> None:
+    """C[:,ns:ne] = A[g] B[:,ns:ne]:  dA[g] = dC[:,ns:ne] B[:,ns:ne]^T (2D x 2D),
+    dB[:,ns:ne] = A[g]^T dC[:,ns:ne] (3D x 2D). Columns past offs[-1] get zero gradient."""
+    if mat_a.size(0) != offs.numel():
+        raise RuntimeError("matrix batch sizes have to match")
+    g = _grad_operand(grad_out, mat_a)
+    if grad_a is not None:
+        forward_into(g, mat_b.transpose(-2, -1), offs, grad_a)
+    if grad_b is not None:
+        grad_b.zero_()
+        forward_into(mat_a.transpose(-2, -1), g, offs, grad_b)
+
+
 class _GroupedMM(torch.autograd.Function):
     @staticmethod
     def forward(ctx, mat_a, mat_b, offs, bias, out_dtype):  # type: ignore[override]
@@ -194,45 +252,17 @@ class _GroupedMM(torch.autograd.Function):
         if grad_out.numel() == 0 or mat_a.size(-1) == 0:
             return (torch.zeros_like(mat_a) if need_a else None, torch.zeros_like(mat_b) if need_b else None,
                     None, None, None)
-        g = _stride_valid(grad_out)
-        if g.dtype != mat_a.dtype:
-            g = g.to(mat_a.dtype)
         a_is_2d, b_is_2d = ctx.forms
         grad_a = torch.empty_like(mat_a) if need_a else None
         grad_b = torch.empty_like(mat_b) if need_b else None
-        a_t, b_t = mat_a.transpose(-2, -1), mat_b.transpose(-2, -1)
         if not a_is_2d and not b_is_2d:
-            # C[g] = A[g] B[g]:  dA[g] = dC[g] B[g]^T,  dB[g] = A[g]^T dC[g]
-            if need_a:
-                forward_into(g, b_t, None, grad_a)
-            if need_b:
-                forward_into(a_t, g, None, grad_b)
+            grouped_mm_3d3d_backward(mat_a, mat_b, grad_out, grad_a, grad_b)
         elif a_is_2d and not b_is_2d:
-            # C[rows_g] = A[rows_g] B[g]:  dA[rows_g] = dC[rows_g] B[g]^T (2D x 3D),
-            # dB[g] = A[rows_g]^T dC[rows_g] (2D x 2D; empty groups give zeros). Rows past offs[-1]
-            # belong to no group: their gradient is zero.
-            if need_a:
-                grad_a.zero_()
-                forward_into(g, b_t, offs, grad_a)
-            if need_b:
-                forward_into(a_t, g, offs, grad_b)
+            grouped_mm_2d3d_backward(mat_a, mat_b, offs, grad_out, grad_a, grad_b)
         elif a_is_2d and b_is_2d:
-            # C[g] = A[:,ks:ke] B[ks:ke,:]:  dA[:,ks:ke] = dC[g] B[ks:ke,:]^T (3D x 2D),
-            # dB[ks:ke,:] = A[:,ks:ke]^T dC[g] (2D x 3D).
-            if need_a:
-                grad_a.zero_()
-                forward_into(g, b_t, offs, grad_a)
-            if need_b:
-                grad_b.zero_()
-                forward_into(a_t, g, offs, grad_b)
+            grouped_mm_2d2d_backward(mat_a, mat_b, offs, grad_out, grad_a, grad_b)
         else:
-            # C[:,ns:ne] = A[g] B[:,ns:ne]:  dA[g] = dC[:,ns:ne] B[:,ns:ne]^T (2D x 2D),
-            # dB[:,ns:ne] = A[g]^T dC[:,ns:ne] (3D x 2D).
-            if need_a:
-                forward_into(g, b_t, offs, grad_a)
-            if need_b:
-                grad_b.zero_()
-                forward_into(a_t, g, offs, grad_b)
+            grouped_mm_3d2d_backward(mat_a, mat_b, offs, grad_out, grad_a, grad_b)
         return grad_a, grad_b, None, None, None
 
 

@@ -136,3 +136,53 @@ def test_readme_example():
     a = torch.randn((int(offs[-1].item()), 64), device=DEV, dtype=torch.bfloat16)
     b = torch.randn((sizes.numel(), 64, 48), device=DEV, dtype=torch.bfloat16)
     torch.testing.assert_close(grouped_mm(a, b, offs=offs), _ref_2d3d(a, b, offs), atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("form", ["3d3d", "2d3d", "2d2d", "3d2d"])
+@pytest.mark.parametrize("need", ["both", "a_only", "b_only"])
+def test_kernel_level_backward_functions_write_every_element(form, need):
+    """The four ``*_backward`` functions of the kernels module (the names the reference's api.py
+    imports from its kernels.py, kernels.py:1093-1390) get buffers from ``torch.empty_like`` and have
+    to define them completely, zeros included; trailing rows / columns / k-indices past offs[-1]
+    belong to no group."""
+    from grouped_mm_bf16 import kernels
+
+    g = torch.Generator(device=DEV).manual_seed(71)
+    sizes = [7, 0, 1, 13, 11]
+    extra = 3  # ragged extent beyond offs[-1]
+    total = sum(sizes) + extra
+    rnd = lambda *shape: torch.randn(shape, device=DEV, generator=g).bfloat16()  # noqa: E731
+    offs = _offs(sizes)
+    if form == "3d3d":
+        a, b, offs, ref_fn = rnd(3, 17, 24), rnd(3, 24, 40), None, torch.bmm
+    elif form == "2d3d":
+        a, b, ref_fn = rnd(total, 24), rnd(5, 24, 40), _ref_2d3d
+    elif form == "2d2d":
+        a, b, ref_fn = rnd(total, 16).t(), rnd(total, 24), _ref_2d2d
+    else:
+        a, b, ref_fn = rnd(5, 17, 24), rnd(total, 24).t(), _ref_3d2d
+    a2, b2 = a.float().clone().requires_grad_(True), b.float().clone().requires_grad_(True)
+    ref = ref_fn(a2, b2) if offs is None else ref_fn(a2, b2, offs)
+    if form == "2d3d":
+        ref = ref[: sum(sizes)]          # rows past offs[-1] are undefined in the forward result
+    elif form == "3d2d":
+        ref = ref[:, : sum(sizes)]
+    w = torch.randn(ref.shape, device=DEV, generator=g).bfloat16()
+    da_ref, db_ref = torch.autograd.grad((ref * w.float()).sum(), [a2, b2])
+    grad_out = w
+    if form == "2d3d":                   # the operator's output has `total` rows; pad the incoming gradient
+        grad_out = torch.cat([w, torch.zeros((extra, w.size(1)), device=DEV, dtype=w.dtype)])
+    elif form == "3d2d":
+        grad_out = torch.cat([w, torch.zeros((w.size(0), extra), device=DEV, dtype=w.dtype)], dim=1)
+    grad_a = torch.full_like(a, float("nan")) if need != "b_only" else None
+    grad_b = torch.full_like(b, float("nan")) if need != "a_only" else None
+    if form == "3d3d":
+        kernels.grouped_mm_3d3d_backward(a, b, grad_out, grad_a, grad_b)
+    else:
+        getattr(kernels, f"grouped_mm_{form}_backward")(a, b, offs, grad_out, grad_a, grad_b)
+    if grad_a is not None:
+        assert grad_a.stride() == a.stride() and not torch.isnan(grad_a).any()
+        torch.testing.assert_close(grad_a.float(), da_ref, atol=0.15, rtol=2e-2)
+    if grad_b is not None:
+        assert grad_b.stride() == b.stride() and not torch.isnan(grad_b).any()
+        torch.testing.assert_close(grad_b.float(), db_ref, atol=0.15, rtol=2e-2)
