@@ -162,11 +162,17 @@ def test_kernel_level_backward_functions_write_every_element(form, need):
     else:
         a, b, ref_fn = rnd(5, 17, 24), rnd(total, 24).t(), _ref_3d2d
     a2, b2 = a.float().clone().requires_grad_(True), b.float().clone().requires_grad_(True)
-    ref = ref_fn(a2, b2) if offs is None else ref_fn(a2, b2, offs)
-    if form == "2d3d":
-        ref = ref[: sum(sizes)]          # rows past offs[-1] are undefined in the forward result
+    valid = sum(sizes)
+    # The stock-torch references look the group of every row / column up: give them only the part
+    # of the ragged extent that belongs to a group (the rest has no group and gets zero gradient).
+    if form == "3d3d":
+        ref = ref_fn(a2, b2)
+    elif form == "2d3d":
+        ref = ref_fn(a2[:valid], b2, offs)
     elif form == "3d2d":
-        ref = ref[:, : sum(sizes)]
+        ref = ref_fn(a2, b2[:, :valid], offs)
+    else:
+        ref = ref_fn(a2, b2, offs)  # masks by k-range, no lookup
     w = torch.randn(ref.shape, device=DEV, generator=g).bfloat16()
     da_ref, db_ref = torch.autograd.grad((ref * w.float()).sum(), [a2, b2])
     grad_out = w
