@@ -81,3 +81,22 @@ def test_output_geometry_pads_leading_stride_to_16_bytes():
         output_geometry((5, 32, 48), (48, 32), 4, 2)
     with pytest.raises(RuntimeError, match="batched dimension has to match"):
         output_geometry((3, 4, 8), (2, 8, 4), None, 2)
+
+
+def test_kernels_module_has_the_eight_names_the_reference_api_imports():
+    """grouped_mm_bf16/api.py:8-17 imports four forward and four backward functions from kernels."""
+    import inspect
+
+    from grouped_mm_bf16 import kernels
+
+    for form in ("3d3d", "2d3d", "2d2d", "3d2d"):
+        fwd = getattr(kernels, f"grouped_mm_{form}")
+        bwd = getattr(kernels, f"grouped_mm_{form}_backward")
+        n_fwd, n_bwd = len(inspect.signature(fwd).parameters), len(inspect.signature(bwd).parameters)
+        assert (n_fwd, n_bwd) == ((3, 5) if form == "3d3d" else (4, 6))
+    a = torch.zeros((4, 8), dtype=torch.bfloat16)
+    b = torch.zeros((2, 8, 8), dtype=torch.bfloat16)
+    offs = torch.tensor([2, 4], dtype=torch.int32)
+    with pytest.raises(RuntimeError, match="GPU-only"):
+        kernels.grouped_mm_2d3d_backward(a, b, offs, torch.zeros((4, 8), dtype=torch.bfloat16),
+                                         torch.empty_like(a), torch.empty_like(b))
