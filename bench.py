@@ -48,7 +48,7 @@ UNIT = "TFLOP/s"
 
 # DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of the tcgen05 kernel,
 # from an ncu capture; see profiles/. None until captured for that workload.
-NCU_TRAFFIC_BYTES = {"mixtral": 4.101e9}  # pair kernel, full-size launch; summary kept under profiles/
+NCU_TRAFFIC_BYTES = {"mixtral": 4.312e9}  # pair kernel, full-size launch; summary kept under profiles/
 
 
 def read_peaks():
