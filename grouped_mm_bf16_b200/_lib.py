@@ -33,6 +33,7 @@ EXPORTED_SYMBOLS = (
     "gmm_error_string",
     "gmm_last_cuda_error",
     "gmm_workspace_bytes",
+    "gmm_group_maps_bytes",
     "grouped_mm_3d3d",
     "grouped_mm_2d2d",
     "grouped_mm_2d3d",
@@ -67,6 +68,8 @@ class GmmLaunch(ctypes.Structure):
         ("workspace", ctypes.c_void_p),
         ("workspace_bytes", ctypes.c_size_t),
         ("flags", ctypes.c_uint32),
+        ("group_maps", ctypes.c_void_p),
+        ("group_maps_bytes", ctypes.c_size_t),
     ]
 
 
@@ -97,6 +100,8 @@ def load() -> ctypes.CDLL:
         lib.gmm_last_cuda_error.argtypes = []
         lib.gmm_workspace_bytes.restype = ctypes.c_size_t
         lib.gmm_workspace_bytes.argtypes = []
+        lib.gmm_group_maps_bytes.restype = ctypes.c_size_t
+        lib.gmm_group_maps_bytes.argtypes = [ctypes.c_int32]
         lib.grouped_mm_3d3d.restype = ctypes.c_int
         lib.grouped_mm_3d3d.argtypes = [tp, tp, tp, lp]
         for name in ("grouped_mm_2d2d", "grouped_mm_2d3d", "grouped_mm_3d2d", "grouped_mm_2d3d_swiglu"):

@@ -148,6 +148,8 @@ def _launch(form: int, mat_a: torch.Tensor, mat_b: torch.Tensor, offs: Optional[
         raise RuntimeError("grouped_mm_b200 is GPU-only; CPU tensors are not supported")
     if _worth_relayout(form, mat_a, mat_b, out):
         mat_a, mat_b = tensor_core_layouts(form, mat_a, mat_b)
+    if offs is not None:
+        offs = offs.contiguous()  # the library reads n_groups consecutive int32 values
     dev = mat_a.device
     # The library launches on the current device: switch only when the tensors live elsewhere.
     switch = dev.index is not None and dev.index != torch.cuda.current_device()
@@ -161,6 +163,14 @@ def _launch(form: int, mat_a: torch.Tensor, mat_b: torch.Tensor, offs: Optional[
         launch.workspace = ws.data_ptr()
         launch.workspace_bytes = ws.numel() * 4
         launch.flags = _flags(mat_a.dtype)
+        maps = None
+        if form == _lib.FORM_2D2D and offs.numel() > 0:
+            # Scratch for the per-group tensor maps of the K-ragged tensor-core kernels: taken from
+            # torch's caching allocator per call, so that calls on different streams never share it
+            # and the block is not handed out again before this stream has finished with it.
+            maps = torch.empty(int(lib.gmm_group_maps_bytes(offs.numel())), dtype=torch.uint8, device=dev)
+            launch.group_maps = maps.data_ptr()
+            launch.group_maps_bytes = maps.numel()
         a, b, c = _desc(mat_a), _desc(mat_b), _desc(out)
         if form == _lib.FORM_3D3D:
             rc = lib.grouped_mm_3d3d(ctypes.byref(a), ctypes.byref(b), ctypes.byref(c), ctypes.byref(launch))
@@ -226,6 +236,7 @@ def grouped_mm_2d3d_swiglu(mat_a: torch.Tensor, gate_up: torch.Tensor, offs: tor
     if not (mat_a.is_cuda and gate_up.is_cuda and out.is_cuda):
         raise RuntimeError("grouped_mm_b200 is GPU-only; CPU tensors are not supported")
     dev = mat_a.device
+    offs = offs.contiguous()
     with torch.cuda.device(dev):
         ws = workspace(dev)
         launch = _lib.GmmLaunch()

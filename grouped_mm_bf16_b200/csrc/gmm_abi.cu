@@ -408,7 +408,7 @@ int launch_swiglu_t(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensor
 }
 
 int launch_fast(const CanonProblem& p_in, const FastPlan& plan, const DeviceInfo& d, cudaStream_t st,
-                bool swiglu = false) {
+                bool swiglu = false, void* group_maps = nullptr) {
   CanonProblem p = p_in;
   const int bm = plan.pair ? kPairBM : kBM;
   p.panel = choose_panel(p);
@@ -456,6 +456,17 @@ int launch_fast(const CanonProblem& p_in, const FastPlan& plan, const DeviceInfo
   fp.b_mn = plan.b_mn;
   fp.c_tma = c_tma ? 1 : 0;
   fp.idesc = make_idesc(p.in_dtype, plan.a_mn, plan.b_mn, plan.pair ? 256 : 128);
+  fp.maps_a = fp.maps_b = nullptr;
+  if (p.mode == MODE_KRAGGED) {
+    // Per-group copies of both maps, each ending at its group's end along K, written on the device
+    // from `offs` ahead of the GEMM kernel on the same stream.
+    fp.maps_a = reinterpret_cast<const CUtensorMap*>(group_maps);
+    fp.maps_b = fp.maps_a + p.G;
+    build_group_maps_kernel<<<(p.G + 127) / 128, 128, 0, st>>>(ta, tb, p.offs, p.G, p.K,
+                                                              const_cast<CUtensorMap*>(fp.maps_a),
+                                                              const_cast<CUtensorMap*>(fp.maps_b));
+    GMM_CUDA_TRY(cudaGetLastError());
+  }
   if (swiglu) {
     switch (p.out_dtype) {
       case DT_BF16: return launch_swiglu_t<__nv_bfloat16>(ta, tb, tc, fp, plan.pair, grid, st);
@@ -488,7 +499,9 @@ int launch_fast(const CanonProblem& p_in, const FastPlan& plan, const DeviceInfo
                                 : launch_fast_kr<false>(ta, tb, tc, fp, grid, st);
 }
 
-constexpr size_t kWorkspaceBytes = 256;
+constexpr size_t kStatusBytes = 256;  // the workspace of every form: the status word and padding
+
+size_t group_maps_bytes(int n_groups) { return n_groups > 0 ? 2 * sizeof(CUtensorMap) * (size_t)n_groups : 0; }
 
 int run(int form, const gmm_tensor_t* a, const gmm_tensor_t* b, const int32_t* offs, int n_groups,
         const gmm_tensor_t* out, const gmm_launch_t* launch, bool swiglu = false) {
@@ -498,7 +511,7 @@ int run(int form, const gmm_tensor_t* a, const gmm_tensor_t* b, const int32_t* o
   int rc = canonicalise(form, a, b, offs, n_groups, out, &p, &nothing, true, swiglu);
   if (rc != GMM_OK) return rc;
   if (nothing) return GMM_OK;
-  if (!launch->workspace || launch->workspace_bytes < kWorkspaceBytes ||
+  if (!launch->workspace || launch->workspace_bytes < kStatusBytes ||
       (reinterpret_cast<uintptr_t>(launch->workspace) & 255u))
     return GMM_ERR_WORKSPACE;
   p.status = reinterpret_cast<int*>(launch->workspace);
@@ -514,7 +527,12 @@ int run(int form, const gmm_tensor_t* a, const gmm_tensor_t* b, const int32_t* o
   const FastPlan plan =
       (launch->flags & GMM_FLAG_FORCE_GENERIC) ? FastPlan() : plan_fast(p, launch->flags, swiglu);
   if (swiglu) return plan.ok ? launch_fast(p, plan, d, st, true) : GMM_ERR_NOT_FUSABLE;
-  return plan.ok ? launch_fast(p, plan, d, st) : launch_generic(p, d, st);
+  if (!plan.ok) return launch_generic(p, d, st);
+  if (p.mode == MODE_KRAGGED &&
+      (!launch->group_maps || launch->group_maps_bytes < group_maps_bytes(p.G) ||
+       (reinterpret_cast<uintptr_t>(launch->group_maps) & 127u)))
+    return GMM_ERR_WORKSPACE;
+  return launch_fast(p, plan, d, st, false, launch->group_maps);
 }
 
 // ------------------------------------------------------------------ library-owned scratch
@@ -525,6 +543,7 @@ int run(int form, const gmm_tensor_t* a, const gmm_tensor_t* b, const int32_t* o
 // process exits. In host code the array's name only stands for the symbol; the device address
 // comes from cudaGetSymbolAddress(), once per device, with that device current.
 constexpr size_t kStaticScratchBytes = 256;
+static_assert(kStatusBytes <= kStaticScratchBytes, "the row-ragged form's scratch need must fit the library-owned array");
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 struct StaticScratch {
@@ -584,7 +603,7 @@ const char* gmm_error_string(int status) {
     case GMM_ERR_INVALID_ARGUMENT: return "invalid argument (null pointer, rank, size or shape mismatch)";
     case GMM_ERR_UNSUPPORTED_DTYPE: return "unsupported dtype (expected bf16, fp16 or fp32)";
     case GMM_ERR_TOO_MANY_GROUPS: return "Can't process more than 1024 groups";
-    case GMM_ERR_WORKSPACE: return "workspace missing, misaligned or too small";
+    case GMM_ERR_WORKSPACE: return "workspace (or, for grouped_mm_2d2d, group_maps) missing, misaligned or too small";
     case GMM_ERR_CUDA: return "CUDA call failed";
     case GMM_ERR_NOT_SM100: return "device is not compute capability 10.x (B200)";
     case GMM_ERR_DEVICE_WAIT: return "a bounded wait inside the kernel gave up; outputs are invalid";
@@ -596,7 +615,9 @@ const char* gmm_error_string(int status) {
 
 const char* gmm_last_cuda_error(void) { return g_last_cuda_error.c_str(); }
 
-size_t gmm_workspace_bytes(void) { return kWorkspaceBytes; }
+size_t gmm_workspace_bytes(void) { return kStatusBytes; }
+
+size_t gmm_group_maps_bytes(int32_t n_groups) { return group_maps_bytes(n_groups); }
 
 int grouped_mm_3d3d(const gmm_tensor_t* a, const gmm_tensor_t* b, const gmm_tensor_t* out,
                     const gmm_launch_t* launch) {
@@ -626,25 +647,30 @@ int grouped_mm_2d2d(const gmm_tensor_t* a, const gmm_tensor_t* b, const int32_t*
 int grouped_mm_2d3d_static_scratch(const gmm_tensor_t* a, const gmm_tensor_t* b, const int32_t* offs,
                                    int32_t n_groups, const gmm_tensor_t* out, void* stream, uint32_t flags,
                                    void** scratch_address) {
-  // The scratch need of a launch must fit the fixed array; refuse rather than overrun it.
-  if (kWorkspaceBytes > kStaticScratchBytes) {
-    g_last_cuda_error = "scratch requirement exceeds the 256-byte library-owned scratch";
-    return GMM_ERR_WORKSPACE;
-  }
+  // Check the arguments before touching the shared block: a rejected call, or one with no work,
+  // must leave the status word of an earlier call as it is.
+  CanonProblem p;
+  bool nothing;
+  int rc = canonicalise(1, a, b, offs, n_groups, out, &p, &nothing, true);
+  if (rc != GMM_OK) return rc;
   int dev = 0;
   GMM_CUDA_TRY(cudaGetDevice(&dev));
   if (dev < 0 || dev >= kMaxDevices) return GMM_ERR_INVALID_ARGUMENT;
   void* scratch = nullptr;
-  int rc = static_scratch(dev, &scratch);
+  rc = static_scratch(dev, &scratch);
   if (rc != GMM_OK) return rc;
   if (scratch_address) *scratch_address = scratch;
-  // The block keeps whatever the previous call left; the status word has to start at zero.
-  GMM_CUDA_TRY(cudaMemsetAsync(scratch, 0, kStaticScratchBytes, reinterpret_cast<cudaStream_t>(stream)));
+  if (nothing) return GMM_OK;
+  // The block keeps whatever the previous call left. Only the status word has to start at zero;
+  // a code an earlier call left there unread is lost at this point.
+  GMM_CUDA_TRY(cudaMemsetAsync(scratch, 0, sizeof(int), reinterpret_cast<cudaStream_t>(stream)));
   gmm_launch_t launch;
   launch.stream = stream;
   launch.workspace = scratch;
   launch.workspace_bytes = kStaticScratchBytes;
   launch.flags = flags;
+  launch.group_maps = nullptr;  // the row-ragged form needs none
+  launch.group_maps_bytes = 0;
   return run(1, a, b, offs, n_groups, out, &launch);
 }
 

@@ -81,7 +81,53 @@ struct FastParams {
   int b_mn;        // 1: B is MN-major in memory (row-major [K,N]);    0: K-major
   int c_tma;       // 1: the output has a tensor map (unit column stride, 16-byte aligned rows): whole
                    //    32-row x 128-byte pieces of a tile are written with TMA stores
+  // K-ragged mode only: one tensor map per group and operand, in global memory, written by
+  // build_group_maps_kernel just before this launch. Map g equals the operand's map except that
+  // its K extent ends at the group's end, so a k-block that reaches past the group arrives with
+  // zeros in the rows that belong to the next group and contributes exactly nothing.
+  const CUtensorMap* maps_a;
+  const CUtensorMap* maps_b;
 };
+
+// Writes the per-group tensor maps of the K-ragged mode: thread g copies both operands' maps and
+// sets their K extent (dimension 1: both operands are MN-major there) to the clamped end of group g.
+// An empty group gets extent 1; no copy is ever issued with its maps.
+__global__ void build_group_maps_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                                        const __grid_constant__ CUtensorMap tmap_b, const int* __restrict__ offs,
+                                        int n_groups, int k_total, CUtensorMap* maps_a, CUtensorMap* maps_b) {
+  const int g = blockIdx.x * blockDim.x + threadIdx.x;
+  if (g >= n_groups) return;
+  int e = offs[g];
+  e = e < 0 ? 0 : (e > k_total ? k_total : e);
+  const uint32_t extent = e > 0 ? (uint32_t)e : 1u;
+  const uint4* src_a = reinterpret_cast<const uint4*>(&tmap_a);
+  const uint4* src_b = reinterpret_cast<const uint4*>(&tmap_b);
+  uint4* dst_a = reinterpret_cast<uint4*>(maps_a + g);
+  uint4* dst_b = reinterpret_cast<uint4*>(maps_b + g);
+#pragma unroll
+  for (int i = 0; i < (int)(sizeof(CUtensorMap) / sizeof(uint4)); ++i) {
+    dst_a[i] = src_a[i];
+    dst_b[i] = src_b[i];
+  }
+  tensormap_set_dim1(maps_a + g, extent);
+  tensormap_set_dim1(maps_b + g, extent);
+  tensormap_fence_release();
+}
+
+// Producer give-up path: waits, for a bounded time per stage, until the copies requested so far
+// have landed. `s` and `ph` are the producer's ring position: stages before `s` were last requested
+// in the phase of parity `ph`, the others in the phase before (never, on the first trip round the
+// ring: waiting for the phase before a barrier's first returns at once).
+template <int STAGES>
+__device__ __forceinline__ void drain_ring(uint64_t* full, int s, uint32_t ph) {
+  for (int i = 0; i < STAGES; ++i) {
+    const uint32_t parity = (i < s) ? ph : (ph ^ 1u);
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000LL) {
+      if (mbar_try_wait(&full[i], parity)) break;
+    }
+  }
+}
 
 // Status codes written to CanonProblem::status when a bounded wait gives up.
 enum FastStatus : int {
@@ -361,6 +407,9 @@ gmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
+      const CUtensorMap* ta = &tmap_a;
+      const CUtensorMap* tb = &tmap_b;
+      int map_g = -1;
       for (int round = 0; ok; ++round) {
         const int t = tile_of_round<KRAGGED>(round, blockIdx.x, gridDim.x);
         if (t >= total) break;
@@ -368,6 +417,15 @@ gmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const int nkb = (ti.klen + BK - 1) / BK;
         const int az = a_batched ? ti.g : 0;
         const int bz = b_batched ? ti.g : 0;
+        if constexpr (KRAGGED) {
+          if (nkb > 0 && ti.g != map_g) {
+            map_g = ti.g;
+            ta = fp.maps_a + map_g;
+            tb = fp.maps_b + map_g;
+            tensormap_fence_acquire(ta);
+            tensormap_fence_acquire(tb);
+          }
+        }
         for (int kb = 0; kb < nkb; ++kb) {
           if (!mbar_wait(&tail.empty[s], ph ^ 1, abort_flag)) {
             atomicCAS(p.status, 0, ST_PRODUCER_TIMEOUT);
@@ -378,8 +436,8 @@ gmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const int k = ti.k0 + kb * BK;
           uint8_t* sa = smem_a + s * kAStageBytes;
           uint8_t* sb = smem_b + s * kBStageBytes;
-          auto load_a = [&](void* dst, int x, int y) { tma_load_3d(dst, &tmap_a, &tail.full[s], x, y, az); };
-          auto load_b = [&](void* dst, int x, int y) { tma_load_3d(dst, &tmap_b, &tail.full[s], x, y, bz); };
+          auto load_a = [&](void* dst, int x, int y) { tma_load_3d(dst, ta, &tail.full[s], x, y, az); };
+          auto load_b = [&](void* dst, int x, int y) { tma_load_3d(dst, tb, &tail.full[s], x, y, bz); };
           if (!fp.a_mn) {
             load_a(sa, k, ti.m0);
           } else {
@@ -407,84 +465,54 @@ gmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           if (++s == kStages) { s = 0; ph ^= 1; }
         }
       }
-      if (!ok) {
-        // Give copies already in flight a bounded time to land before the CTA exits.
-        for (int i = 0; i < kStages; ++i) {
-          const long long t0 = clock64();
-          while (clock64() - t0 < 2000000LL) {
-            if (mbar_try_wait(&tail.full[i], 0) || mbar_try_wait(&tail.full[i], 1)) break;
-          }
-        }
-      }
+      // After a give-up: a bounded time for the copies already requested to land before the CTA exits.
+      if (!ok) drain_ring<kStages>(tail.full, s, ph);
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer (lane 0 issues)
+    // ------------------------------------------------------------ MMA issuer (one thread)
     // Descriptor geometry. K-major tile: rows of 128 B, 8-row swizzle atoms 1024 B apart; one
     // k-step (16 16-bit or 8 32-bit elements) advances 32 B inside the swizzled row. MN-major
     // tile: chunks of [BK k-rows][128 B] covering 128 B of the MN dimension each; chunks are
     // CHUNK_BYTES apart (leading offset), 8-k-row atoms 1024 B apart (stride offset); a k-step
     // advances UMMA_K rows of 128 B. An MN-major 32-bit operand is swizzled in 32-byte units over
     // 4-row atoms instead (the tensor map loads it that way), so its atoms are 512 B apart.
-    const uint32_t a_lbo = fp.a_mn ? EG::CHUNK_BYTES : 16;
-    const uint32_t b_lbo = fp.b_mn ? EG::CHUNK_BYTES : 16;
-    const uint32_t a_sbo = (ES == 4 && fp.a_mn) ? 512 : 1024;
-    const uint32_t b_sbo = (ES == 4 && fp.b_mn) ? 512 : 1024;
-    const uint32_t a_swz = (ES == 4 && fp.a_mn) ? kSwizzle128BBase32B : kSwizzle128B;
-    const uint32_t b_swz = (ES == 4 && fp.b_mn) ? kSwizzle128BBase32B : kSwizzle128B;
-    const uint32_t a_kstep = fp.a_mn ? (EG::UMMA_K * 128) : 32;
-    const uint32_t b_kstep = fp.b_mn ? (EG::UMMA_K * 128) : 32;
-    int s = 0;
-    uint32_t ph = 0;
-    int it = 0;
-    bool ok = true;
-    for (; ok; ++it) {
-      const int t = tile_of_round<KRAGGED>(it, blockIdx.x, gridDim.x);
-      if (t >= total) break;
-      const int klen = tile_klen(p, tail.sched, t);  // the issuer needs no tile coordinates
-      const int nkb = (klen + BK - 1) / BK;
-      const int buf = it & 1;
-      const uint32_t aph = (it >> 1) & 1;
-      if (!mbar_wait(&tail.acc_empty[buf], aph ^ 1, abort_flag)) {
-        if (lane == 0) atomicCAS(p.status, 0, ST_MMA_TIMEOUT);
-        ok = false;
-        break;
-      }
-      tcgen05_fence_after_sync();
-      const uint32_t d_tmem = tmem_base + buf * kBN;
-      for (int kb = 0; kb < nkb; ++kb) {
-        if (!mbar_wait(&tail.full[s], ph, abort_flag)) {
-          if (lane == 0) atomicCAS(p.status, 0, ST_MMA_TIMEOUT + 0x10);
-          ok = false;
+    // In K-ragged mode the k-rows past a group's end arrive as zeros (per-group tensor maps), so
+    // the last k-block of a group needs no special treatment here.
+    if (lane == 0) {
+      const uint32_t a_lbo = fp.a_mn ? EG::CHUNK_BYTES : 16;
+      const uint32_t b_lbo = fp.b_mn ? EG::CHUNK_BYTES : 16;
+      const uint32_t a_sbo = (ES == 4 && fp.a_mn) ? 512 : 1024;
+      const uint32_t b_sbo = (ES == 4 && fp.b_mn) ? 512 : 1024;
+      const uint32_t a_swz = (ES == 4 && fp.a_mn) ? kSwizzle128BBase32B : kSwizzle128B;
+      const uint32_t b_swz = (ES == 4 && fp.b_mn) ? kSwizzle128BBase32B : kSwizzle128B;
+      const uint32_t a_kstep = fp.a_mn ? (EG::UMMA_K * 128) : 32;
+      const uint32_t b_kstep = fp.b_mn ? (EG::UMMA_K * 128) : 32;
+      int s = 0;
+      uint32_t ph = 0;
+      int it = 0;
+      bool ok = true;
+      for (; ok; ++it) {
+        const int t = tile_of_round<KRAGGED>(it, blockIdx.x, gridDim.x);
+        if (t >= total) break;
+        const int klen = tile_klen(p, tail.sched, t);  // the issuer needs no tile coordinates
+        const int nkb = (klen + BK - 1) / BK;
+        const int buf = it & 1;
+        const uint32_t aph = (it >> 1) & 1;
+        if (!mbar_wait(&tail.acc_empty[buf], aph ^ 1, abort_flag)) {
+          atomicCAS(p.status, 0, ST_MMA_TIMEOUT);
           break;
         }
         tcgen05_fence_after_sync();
-        uint8_t* sa = smem_a + s * kAStageBytes;
-        uint8_t* sb = smem_b + s * kBStageBytes;
-        if constexpr (KRAGGED) {
-          // The last k-block of a group over-reads k-rows of the next group. Both operands are
-          // MN-major here, so k-rows are whole 128-byte lines: rows [r, BK) of every chunk form
-          // one contiguous range, zeroed before the MMA so they contribute exactly 0.
-          const int r = klen - kb * BK;
-          if (r < BK) {
-            const int n16 = (BK - r) * 8;  // 16-byte words per chunk
-            const uint4 z = make_uint4(0, 0, 0, 0);
-#pragma unroll
-            for (int c = 0; c < kBM / EG::CHUNK_W; ++c) {
-              uint4* q = reinterpret_cast<uint4*>(sa + c * EG::CHUNK_BYTES + r * 128);
-              for (int i = lane; i < n16; i += 32) q[i] = z;
-            }
-#pragma unroll
-            for (int c = 0; c < kBN / EG::CHUNK_W; ++c) {
-              uint4* q = reinterpret_cast<uint4*>(sb + c * EG::CHUNK_BYTES + r * 128);
-              for (int i = lane; i < n16; i += 32) q[i] = z;
-            }
-            fence_proxy_async_smem();
+        const uint32_t d_tmem = tmem_base + buf * kBN;
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!mbar_wait(&tail.full[s], ph, abort_flag)) {
+            atomicCAS(p.status, 0, ST_MMA_TIMEOUT + 0x10);
+            ok = false;
+            break;
           }
-          __syncwarp();
-        }
-        if (lane == 0) {
-          const uint64_t a_desc = make_smem_desc_sw128(smem_u32(sa), a_lbo, a_sbo, a_swz);
-          const uint64_t b_desc = make_smem_desc_sw128(smem_u32(sb), b_lbo, b_sbo, b_swz);
+          tcgen05_fence_after_sync();
+          const uint64_t a_desc = make_smem_desc_sw128(smem_u32(smem_a + s * kAStageBytes), a_lbo, a_sbo, a_swz);
+          const uint64_t b_desc = make_smem_desc_sw128(smem_u32(smem_b + s * kBStageBytes), b_lbo, b_sbo, b_swz);
 #pragma unroll
           for (int k = 0; k < BK / EG::UMMA_K; ++k) {
             if constexpr (ES == 4)
@@ -495,12 +523,10 @@ gmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                           (kb | k) != 0 ? 1u : 0u);
           }
           umma_commit(&tail.empty[s]);  // frees the stage once these MMAs have read it
+          if (++s == kStages) { s = 0; ph ^= 1; }
         }
-        __syncwarp();
-        if (++s == kStages) { s = 0; ph ^= 1; }
+        if (ok) umma_commit(&tail.acc_full[buf]);
       }
-      if (ok && lane == 0) umma_commit(&tail.acc_full[buf]);
-      __syncwarp();
     }
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5)
@@ -514,7 +540,10 @@ gmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const TileInfo ti = decode_tile<kBM, BNT>(p, tail.sched, t);
       const int buf = it & 1;
       const uint32_t aph = (it >> 1) & 1;
-      if (!mbar_wait(&tail.acc_full[buf], aph, abort_flag, kEpilogueBackoffNs)) {
+      // The lanes poll on their own, so one of them may see the barrier complete just as another
+      // runs out of budget; the vote makes the whole warp take the same way (tcgen05.ld below is
+      // a whole-warp instruction).
+      if (!__all_sync(0xffffffffu, mbar_wait(&tail.acc_full[buf], aph, abort_flag, kEpilogueBackoffNs))) {
         if (lane == 0) atomicCAS(p.status, 0, ST_EPILOGUE_TIMEOUT);
         ok = false;
         break;

@@ -14,12 +14,10 @@
 //   acc_full[b]  one per CTA; same
 //   acc_empty[b] lives in the leader; the 2 x 128 epilogue threads arrive on it
 //
-// K-ragged mode (KRAGGED = true) differs in one respect. The last k-block of a group over-reads
-// k-rows of the next group, and both CTAs have to zero those rows of their own stage before the
-// MMA may read them. So each CTA's loads credit its OWN full[s]; warp 1 of the peer CTA (idle
-// otherwise) waits for its stage, zeroes the tail rows if there are any, and then arrives on
-// peer_ready[s] in the leader; the leader's issuer waits for its own full[s], zeroes its own tail,
-// waits for peer_ready[s] and only then issues.
+// K-ragged mode (KRAGGED = true) loads through per-group tensor maps whose K extent ends at the
+// group's end (FastParams::maps_a / maps_b), so the k-rows a group's last k-block reads past its
+// end arrive as zeros in both CTAs and the main loop is the same as in the other modes; tiles are
+// dealt in cost order (gmm_common.cuh) and an empty group's tiles are stored as zeros.
 #pragma once
 
 #include "gmm_sm100_kernel.cuh"
@@ -38,7 +36,6 @@ struct PairSmemTail {
   uint64_t empty[kPairStages];
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
-  uint64_t peer_ready[kPairStages];  // K-ragged mode only: the peer's stage is loaded and its tail zeroed
   uint32_t tmem_base;
   int abort_flag;
   SchedSmem sched;
@@ -51,22 +48,7 @@ enum PairStatus : int {
   ST_PAIR_PRODUCER_TIMEOUT = 0x201,
   ST_PAIR_MMA_TIMEOUT = 0x202,
   ST_PAIR_EPILOGUE_TIMEOUT = 0x203,
-  ST_PAIR_RELAY_TIMEOUT = 0x204,
 };
-
-// Zeroes k-rows [r, BK) of the MN-major chunks (each [BK k-rows][128 B]) of one 16 KiB stage buffer.
-// Whole-warp call; ends with the proxy fence that makes the zeros visible to the MMA.
-template <int ES>
-__device__ __forceinline__ void zero_tail_rows(uint8_t* stage_buf, int r, int lane) {
-  using EG = ElemGeom<ES>;
-  const int n16 = (EG::BK - r) * 8;  // 16-byte words per chunk
-  const uint4 z = make_uint4(0, 0, 0, 0);
-  for (int c = 0; c < 128 / EG::CHUNK_W; ++c) {
-    uint4* q = reinterpret_cast<uint4*>(stage_buf + c * EG::CHUNK_BYTES + r * 128);
-    for (int i = lane; i < n16; i += 32) q[i] = z;
-  }
-  fence_proxy_async_smem();
-}
 
 // SWIGLU (row-ragged mode): B holds [gate | up], 2 N columns per group; the leader CTA loads the
 // tile's 128 gate columns, its peer the matching 128 up columns, so that every accumulator row holds
@@ -100,7 +82,6 @@ gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     for (int s = 0; s < kPairStages; ++s) {
       mbar_init(&tail.full[s], 1);
       mbar_init(&tail.empty[s], 1);
-      mbar_init(&tail.peer_ready[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tail.acc_full[b], 1);
@@ -131,6 +112,10 @@ gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
+      const CUtensorMap* ta = &tmap_a;
+      const CUtensorMap* tb = &tmap_b;
+      int map_g = -1;
+      const uint32_t full0_leader = map_to_cta(smem_u32(&tail.full[0]), 0);
       for (int round = 0; ok; ++round) {
         const int t = tile_of_round<KRAGGED>(round, pair, n_pairs);
         if (t >= total) break;
@@ -140,25 +125,29 @@ gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         const int bz = KRAGGED ? 0 : ti.g;
         const int row0 = ti.m0 + int(rank) * 128;
         const int col0 = SWIGLU ? (rank ? p.N + ti.n0 : ti.n0) : ti.n0 + int(rank) * kPairBNHalf;
+        if constexpr (KRAGGED) {
+          if (nkb > 0 && ti.g != map_g) {
+            map_g = ti.g;
+            ta = fp.maps_a + map_g;
+            tb = fp.maps_b + map_g;
+            tensormap_fence_acquire(ta);
+            tensormap_fence_acquire(tb);
+          }
+        }
         for (int kb = 0; kb < nkb; ++kb) {
           if (!mbar_wait(&tail.empty[s], ph ^ 1, abort_flag)) {
             atomicCAS(p.status, 0, ST_PAIR_PRODUCER_TIMEOUT);
             ok = false;
             break;
           }
-          uint32_t bar;  // where this CTA's loads are credited
-          if constexpr (KRAGGED) {
-            mbar_arrive_expect_tx(&tail.full[s], kPairStageBytes);
-            bar = smem_u32(&tail.full[s]);
-          } else {
-            if (rank == 0) mbar_arrive_expect_tx(&tail.full[s], 2 * kPairStageBytes);
-            bar = map_to_cta(smem_u32(&tail.full[s]), 0);
-          }
+          // Both CTAs' loads are credited to the leader's full[s].
+          if (rank == 0) mbar_arrive_expect_tx(&tail.full[s], 2 * kPairStageBytes);
+          const uint32_t bar = full0_leader + s * (uint32_t)sizeof(uint64_t);
           const int k = ti.k0 + kb * BK;
           uint8_t* sa = smem_a + s * kPairAStageBytes;
           uint8_t* sb = smem_b + s * kPairBStageBytes;
-          auto load_a = [&](void* dst, int x, int y) { tma_load_3d_pair(dst, &tmap_a, bar, x, y, az); };
-          auto load_b = [&](void* dst, int x, int y) { tma_load_3d_pair(dst, &tmap_b, bar, x, y, bz); };
+          auto load_a = [&](void* dst, int x, int y) { tma_load_3d_pair(dst, ta, bar, x, y, az); };
+          auto load_b = [&](void* dst, int x, int y) { tma_load_3d_pair(dst, tb, bar, x, y, bz); };
           if (!fp.a_mn) {
             load_a(sa, k, row0);
           } else {
@@ -174,10 +163,13 @@ gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           if (++s == kPairStages) { s = 0; ph ^= 1; }
         }
       }
+      // After a give-up: a bounded time for the copies already requested (by either CTA: all are
+      // credited to the leader's barriers) to land before the pair leaves.
+      if (!ok && rank == 0) drain_ring<kPairStages>(tail.full, s, ph);
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer (leader CTA, lane 0)
-    if (rank == 0) {
+    // ------------------------------------------------------------ MMA issuer (leader CTA, one thread)
+    if (rank == 0 && lane == 0) {
       // descriptor geometry: see the single-CTA kernel
       const uint32_t a_lbo = fp.a_mn ? EG::CHUNK_BYTES : 16;
       const uint32_t b_lbo = fp.b_mn ? EG::CHUNK_BYTES : 16;
@@ -199,83 +191,33 @@ gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         const int buf = it & 1;
         const uint32_t aph = (it >> 1) & 1;
         if (!mbar_wait_cluster(&tail.acc_empty[buf], aph ^ 1, abort_flag)) {
-          if (lane == 0) atomicCAS(p.status, 0, ST_PAIR_MMA_TIMEOUT);
-          ok = false;
+          atomicCAS(p.status, 0, ST_PAIR_MMA_TIMEOUT);
           break;
         }
         tcgen05_fence_after_sync();
         const uint32_t d_tmem = tmem_base + buf * kBN;
         for (int kb = 0; kb < nkb; ++kb) {
           if (!mbar_wait(&tail.full[s], ph, abort_flag)) {
-            if (lane == 0) atomicCAS(p.status, 0, ST_PAIR_MMA_TIMEOUT + 0x10);
+            atomicCAS(p.status, 0, ST_PAIR_MMA_TIMEOUT + 0x10);
             ok = false;
             break;
-          }
-          if constexpr (KRAGGED) {
-            const int r = klen - kb * BK;
-            if (r < BK) {
-              zero_tail_rows<ES>(smem_a + s * kPairAStageBytes, r, lane);
-              zero_tail_rows<ES>(smem_b + s * kPairBStageBytes, r, lane);
-            }
-            __syncwarp();
-            if (!mbar_wait_cluster(&tail.peer_ready[s], ph, abort_flag)) {
-              if (lane == 0) atomicCAS(p.status, 0, ST_PAIR_MMA_TIMEOUT + 0x20);
-              ok = false;
-              break;
-            }
           }
           tcgen05_fence_after_sync();
-          if (lane == 0) {
-            const uint64_t a_desc =
-                make_smem_desc_sw128(smem_u32(smem_a + s * kPairAStageBytes), a_lbo, a_sbo, a_swz);
-            const uint64_t b_desc =
-                make_smem_desc_sw128(smem_u32(smem_b + s * kPairBStageBytes), b_lbo, b_sbo, b_swz);
+          const uint64_t a_desc = make_smem_desc_sw128(smem_u32(smem_a + s * kPairAStageBytes), a_lbo, a_sbo, a_swz);
+          const uint64_t b_desc = make_smem_desc_sw128(smem_u32(smem_b + s * kPairBStageBytes), b_lbo, b_sbo, b_swz);
 #pragma unroll
-            for (int k = 0; k < BK / EG::UMMA_K; ++k) {
-              if constexpr (ES == 4)
-                umma_tf32_ss_pair(d_tmem, a_desc + ((k * a_kstep) >> 4), b_desc + ((k * b_kstep) >> 4), fp.idesc,
-                                  (kb | k) != 0 ? 1u : 0u);
-              else
-                umma_f16_ss_pair(d_tmem, a_desc + ((k * a_kstep) >> 4), b_desc + ((k * b_kstep) >> 4), fp.idesc,
-                                 (kb | k) != 0 ? 1u : 0u);
-            }
-            umma_commit_pair(&tail.empty[s], 0x3);  // frees the stage in both CTAs
+          for (int k = 0; k < BK / EG::UMMA_K; ++k) {
+            if constexpr (ES == 4)
+              umma_tf32_ss_pair(d_tmem, a_desc + ((k * a_kstep) >> 4), b_desc + ((k * b_kstep) >> 4), fp.idesc,
+                                (kb | k) != 0 ? 1u : 0u);
+            else
+              umma_f16_ss_pair(d_tmem, a_desc + ((k * a_kstep) >> 4), b_desc + ((k * b_kstep) >> 4), fp.idesc,
+                               (kb | k) != 0 ? 1u : 0u);
           }
-          __syncwarp();
+          umma_commit_pair(&tail.empty[s], 0x3);  // frees the stage in both CTAs
           if (++s == kPairStages) { s = 0; ph ^= 1; }
         }
-        if (ok && lane == 0) umma_commit_pair(&tail.acc_full[buf], 0x3);
-        __syncwarp();
-      }
-    } else if constexpr (KRAGGED) {
-      // -------------------------------------------------------- relay (peer CTA, K-ragged mode)
-      const uint32_t ready_leader0 = map_to_cta(smem_u32(&tail.peer_ready[0]), 0);
-      int s = 0;
-      uint32_t ph = 0;
-      bool ok = true;
-      for (int round = 0; ok; ++round) {
-        const int t = tile_of_round<KRAGGED>(round, pair, n_pairs);
-        if (t >= total) break;
-        const int klen = tile_klen(p, tail.sched, t);
-        const int nkb = (klen + BK - 1) / BK;
-        for (int kb = 0; kb < nkb; ++kb) {
-          if (!mbar_wait(&tail.full[s], ph, abort_flag)) {
-            if (lane == 0) atomicCAS(p.status, 0, ST_PAIR_RELAY_TIMEOUT);
-            ok = false;
-            break;
-          }
-          const int r = klen - kb * BK;
-          if (r < BK) {
-            zero_tail_rows<ES>(smem_a + s * kPairAStageBytes, r, lane);
-            zero_tail_rows<ES>(smem_b + s * kPairBStageBytes, r, lane);
-          }
-          __syncwarp();
-          if (lane == 0) {
-            if (r < BK) mbar_arrive_cluster(ready_leader0 + s * (uint32_t)sizeof(uint64_t));
-            else mbar_arrive_cluster_relaxed(ready_leader0 + s * (uint32_t)sizeof(uint64_t));
-          }
-          if (++s == kPairStages) { s = 0; ph ^= 1; }
-        }
+        if (ok) umma_commit_pair(&tail.acc_full[buf], 0x3);
       }
     }
   } else {
@@ -290,7 +232,8 @@ gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       const TileInfo ti = decode_tile<kPairBM, BNT>(p, tail.sched, t);
       const int buf = it & 1;
       const uint32_t aph = (it >> 1) & 1;
-      if (!mbar_wait(&tail.acc_full[buf], aph, abort_flag, kEpilogueBackoffNs)) {
+      // warp-uniform outcome, as in the single-CTA kernel
+      if (!__all_sync(0xffffffffu, mbar_wait(&tail.acc_full[buf], aph, abort_flag, kEpilogueBackoffNs))) {
         if (lane == 0) atomicCAS(p.status, 0, ST_PAIR_EPILOGUE_TIMEOUT);
         ok = false;
         break;

@@ -126,6 +126,29 @@ __device__ __forceinline__ void tma_store_wait_read() {
 }
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
+// ---------------------------------------------------------------- tensor maps edited on the device
+//
+// A tensor map (128 bytes, in global memory) may have fields rewritten by device code. The writer
+// follows its edits with a release fence of the tensormap proxy; a thread that is about to hand the
+// map to a TMA copy first runs the matching acquire fence on its address.
+
+// Sets the extent of dimension 1 (the dimension after the innermost) of the tiled map at `gmap`.
+__device__ __forceinline__ void tensormap_set_dim1(void* gmap, uint32_t extent) {
+  asm volatile("tensormap.replace.tile.global_dim.global.b1024.b32 [%0], 1, %1;"
+               ::"l"(reinterpret_cast<uint64_t>(gmap)), "r"(extent)
+               : "memory");
+}
+
+__device__ __forceinline__ void tensormap_fence_release() {
+  asm volatile("fence.proxy.tensormap::generic.release.gpu;" ::: "memory");
+}
+
+__device__ __forceinline__ void tensormap_fence_acquire(const void* gmap) {
+  asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;"
+               ::"l"(reinterpret_cast<uint64_t>(gmap))
+               : "memory");
+}
+
 // ---------------------------------------------------------------- tensor memory
 
 // Whole-warp calls (.sync.aligned). The allocated base address is written to *smem_holder.

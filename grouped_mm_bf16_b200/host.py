@@ -107,7 +107,8 @@ def grouped_mm_host(mat_a: torch.Tensor, mat_b: torch.Tensor, offs: torch.Tensor
     last_d2h = None
     for i, (lo, hi) in enumerate(chunks):
         slot = i % _DEPTH
-        r0, r1 = starts[lo], ends[hi - 1]
+        r0 = starts[lo]
+        r1 = max(r0, ends[hi - 1])  # offsets that run backwards make empty groups, never a negative extent
         rows, g = r1 - r0, hi - lo
         with torch.cuda.stream(st.h2d):
             if st.free_evt[slot] is not None:

@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-#define GMM_ABI_VERSION 1
+#define GMM_ABI_VERSION 2
 
 /* Element types (reference: _as_tl_dtype, grouped_mm_bf16/kernels.py:175-182). */
 enum gmm_dtype { GMM_BF16 = 0, GMM_F16 = 1, GMM_F32 = 2 };
@@ -81,6 +81,17 @@ typedef struct gmm_launch {
   void* workspace;
   size_t workspace_bytes;
   uint32_t flags;
+  /*
+   * grouped_mm_2d2d() on the tensor-core path only; NULL / 0 for every other call. Device memory,
+   * 128-byte aligned, at least gmm_group_maps_bytes(n_groups) long, contents irrelevant: the call
+   * first writes one tensor map per group and operand there (each bounded at that group's end of
+   * the ragged K dimension, so that TMA fills what a group's last block reads past its end with
+   * zeros) and its GEMM kernel then loads through them. The buffer must stay untouched until the
+   * call's work on `stream` has finished, and calls that may be in flight at the same time need
+   * separate buffers. Without it such a call returns GMM_ERR_WORKSPACE.
+   */
+  void* group_maps;
+  size_t group_maps_bytes;
 } gmm_launch_t;
 
 int gmm_abi_version(void);
@@ -88,6 +99,8 @@ const char* gmm_error_string(int status);
 /* Text of the last CUDA error seen by the calling thread inside this library ("" if none). */
 const char* gmm_last_cuda_error(void);
 size_t gmm_workspace_bytes(void);
+/* Size of gmm_launch_t.group_maps for a grouped_mm_2d2d() call with n_groups groups (0 if n_groups < 1). */
+size_t gmm_group_maps_bytes(int32_t n_groups);
 
 /*
  * out[g] = a[g] @ b[g]; a [G,M,K], b [G,K,N], out [G,M,N].

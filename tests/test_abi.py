@@ -32,7 +32,7 @@ def test_every_declared_symbol_is_exported(lib):
 
 
 def test_version_and_error_strings(lib):
-    assert lib.gmm_abi_version() == 1
+    assert lib.gmm_abi_version() == 2
     assert lib.gmm_error_string(0) == b"ok"
     assert b"1024 groups" in lib.gmm_error_string(-3)
     assert lib.gmm_workspace_bytes() >= 4
