@@ -41,14 +41,46 @@ ROOT = Path(__file__).resolve().parent
 if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
-from grouped_mm_bf16_b200.workloads import (group_sizes, imbalance, make_workload, partition_groups)  # noqa: E402
+from grouped_mm_bf16_b200.workloads import (group_sizes, imbalance, make_workload, partition_groups,  # noqa: E402
+                                             partition_rows)
 
 METRIC = "useful TFLOP/s, 2Dx3D MoE grouped_mm forward (Mixtral-shape)"
 UNIT = "TFLOP/s"
 
-# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of the tcgen05 kernel,
-# from an ncu capture; see profiles/. None until captured for that workload.
-NCU_TRAFFIC_BYTES = {"mixtral": 4.312e9}  # pair kernel, full-size launch; summary kept under profiles/
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of the tcgen05 kernel comes
+# from an ncu capture whose summary under profiles/ records, beside the figure, a hash of the kernel
+# sources it was taken from; the figure is reported only while the sources still have that hash.
+TRAFFIC_SUMMARIES = {"mixtral": "gmm_sm100_pair_kernel_mixtral.md"}
+
+
+def kernel_sources_hash() -> str:
+    """sha256 over the CUDA sources of the library (names and contents, sorted)."""
+    import hashlib
+
+    h = hashlib.sha256()
+    csrc = ROOT / "grouped_mm_bf16_b200" / "csrc"
+    for f in sorted(list(csrc.glob("*.cu")) + list(csrc.glob("*.cuh"))):
+        h.update(f.name.encode())
+        h.update(f.read_bytes())
+    return h.hexdigest()[:16]
+
+
+def ncu_traffic_bytes(workload: str):
+    """(bytes per launch or None, note) from the workload's ncu summary, if it matches the sources."""
+    import re
+
+    name = TRAFFIC_SUMMARIES.get(workload)
+    path = ROOT / "profiles" / name if name else None
+    if path is None or not path.exists():
+        return None, "no ncu capture of this workload"
+    text = path.read_text()
+    m_bytes = re.search(r"dram_bytes_per_launch:\s*([0-9.eE+]+)", text)
+    m_hash = re.search(r"kernel_sources_sha256_16:\s*([0-9a-f]{16})", text)
+    if not (m_bytes and m_hash):
+        return None, f"profiles/{name} records no traffic figure"
+    if m_hash.group(1) != kernel_sources_hash():
+        return None, f"profiles/{name} was captured from other kernel sources ({m_hash.group(1)}); not carried over"
+    return float(m_bytes.group(1)), f"ncu capture summarised in profiles/{name}"
 
 
 def read_peaks():
@@ -157,6 +189,18 @@ def sum_over_ranks(dist, value: float) -> float:
     return float(t.item())
 
 
+def rank_stats(dist, value: float):
+    """{"min", "median", "max"} of one number per rank (all ranks call; every rank gets the result)."""
+    if dist is None:
+        return {"min": value, "median": value, "max": value}
+    world = dist.get_world_size()
+    mine = torch.tensor([value], dtype=torch.float64, device="cuda")
+    every = [torch.zeros_like(mine) for _ in range(world)]
+    dist.all_gather(every, mine)
+    vals = sorted(float(t.item()) for t in every)
+    return {"min": vals[0], "median": statistics.median(vals), "max": vals[-1]}
+
+
 def time_steps(dist, step_fn, steps: int, warmup: int, sampler=None) -> float:
     """Runs `warmup` untimed and exactly `steps` timed calls; returns ms for the timed region on
     this rank (CUDA events on the launching stream, barrier + synchronize on both sides)."""
@@ -228,6 +272,19 @@ def cpu_oracle_sample(a_cpu, b_cpu, sizes, budget_s: float, workload_rows=None):
     return 2.0 * rows * k * n, dt, f"first {rows} of {of} rows ({rows // len(live)} per group, {len(live)} groups), K={k}, N={n}"
 
 
+def workload_config(args, wl):
+    """`config` of the JSON line: the same for both arms when they run the same workload."""
+    groups = len(wl.sizes) if wl.sizes else wl.mat_a.size(0)
+    return {
+        "workload": f"{args.workload}: form {wl.form}, a {tuple(wl.mat_a.shape)}, b {tuple(wl.mat_b.shape)}, "
+                    f"{groups} groups per GPU, seeded sizes",
+        "sharding": "expert-parallel, one process per GPU, no collective in the timed region",
+        "l2": "inputs larger than L2 (no flush needed)",
+        "reduced": None if (args.dims_scale == 1.0 and args.rows_scale == 1.0) else
+        f"NOT the benchmark size: dims x{args.dims_scale}, rows x{args.rows_scale} (profiling case)",
+    }
+
+
 def run_reference_arm(args):
     """`--impl reference`: the CPU restatement of the path on the host cores."""
     rank = int(os.environ.get("RANK", "0"))
@@ -235,14 +292,30 @@ def run_reference_arm(args):
         return
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    sizes = group_sizes(args.workload, 0)
-    # Up to 4096 rows of every group: per-group GEMMs tall enough for the CPU BLAS to reach its best rate.
-    wl = make_workload(args.workload, "cpu", seed=0, sizes=[min(s, 4096) for s in sizes], dims_scale=args.dims_scale)
-    per_step = max(1.0, min(8.0, 150.0 / max(1, args.steps + args.warmup)))
+    from oracle.grouped_mm_oracle import grouped_mm_oracle  # the checker, timed here as the CPU reference arm
+
+    wl = make_workload(args.workload, "cpu", seed=0, scale=args.rows_scale, dims_scale=args.dims_scale)
+    if wl.form != "2d3d":
+        print(json.dumps({"impl": "reference", "unavailable": "the CPU reference arm times the 2D x 3D form only"}))
+        return
+    # Calibrate on a small sample, then decide: whole passes over the full workload on the timed
+    # steps if the run stays within a few minutes, else a bounded row sample per step.
+    f0, t0, _ = cpu_oracle_sample(wl.mat_a, wl.mat_b, wl.sizes, 1.0)
+    full_pass_s = wl.flops / max(f0 / t0, 1.0)
+    full = full_pass_s * args.steps <= 200.0
     times, flops, desc = [], 0.0, ""
     for i in range(args.warmup + args.steps):
-        f, dt, desc = cpu_oracle_sample(wl.mat_a, wl.mat_b, wl.sizes, per_step, workload_rows=sum(sizes))
-        if i >= args.warmup:
+        if i < args.warmup:
+            cpu_oracle_sample(wl.mat_a, wl.mat_b, wl.sizes, 1.0)  # warm-up: threads and allocator
+            continue
+        if full:
+            t = time.perf_counter()
+            grouped_mm_oracle(wl.mat_a, wl.mat_b, wl.offs)
+            times.append(time.perf_counter() - t)
+            flops, desc = wl.flops, f"the whole workload every timed step: all {sum(wl.sizes)} rows, {len(wl.sizes)} groups"
+        else:
+            per_step = max(1.0, min(8.0, 150.0 / max(1, args.steps)))
+            f, dt, desc = cpu_oracle_sample(wl.mat_a, wl.mat_b, wl.sizes, per_step)
             times.append(dt)
             flops = f
     ms = 1e3 * sum(times) / len(times)
@@ -251,7 +324,8 @@ def run_reference_arm(args):
         "metric": METRIC, "value": value, "unit": UNIT, "impl": "reference", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16 in, f32 accumulate", "data": "synthetic",
-        "config": {"workload": f"{args.workload}: per-group fp32 torch.matmul on CPU, sample = {desc}"},
+        "config": workload_config(args, wl),
+        "reference_detail": f"per-group fp32 torch.matmul on {cores} host threads (CPU restatement of the path); {desc}",
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -269,13 +343,27 @@ def triton_reference_tflops(wl, steps: int, warmup: int):
     pkg = ROOT / "baseline" / "_ref" / "grouped_mm_bf16"
     if not (pkg / "__init__.py").exists():
         return {"unavailable": "baseline/_ref/grouped_mm_bf16 not present"}
+    if max(wl.mat_a.numel(), wl.mat_b.numel()) >= 2 ** 31:
+        # Its kernels index with 32-bit products (g * stride_bg, kernels.py:340-341); on operands of
+        # 2^31 elements or more (the DeepSeek-shape weights) they made an illegal memory access on a
+        # B200. Known from that record; never launched at such a size.
+        return {"unavailable": "reference faults at this size (32-bit index arithmetic past 2^31 elements); not run"}
     try:
         spec = importlib.util.spec_from_file_location("_reference_grouped_mm_bf16", pkg / "__init__.py",
                                                       submodule_search_locations=[str(pkg)])
         mod = importlib.util.module_from_spec(spec)
         sys.modules["_reference_grouped_mm_bf16"] = mod
         spec.loader.exec_module(mod)
-        fn = lambda: mod.grouped_mm(wl.mat_a, wl.mat_b, offs=wl.offs)  # noqa: E731
+        if wl.form == "2d2d" and wl.out_dtype == torch.float32:
+            # its operator rejects an fp32 result for bf16 inputs; its kernel-level function takes one
+            from importlib import import_module
+
+            kernels = import_module("_reference_grouped_mm_bf16.kernels")
+            out32 = torch.empty((wl.offs.numel(), wl.mat_a.size(0), wl.mat_b.size(1)), dtype=torch.float32,
+                                device=wl.mat_a.device)
+            fn = lambda: kernels.grouped_mm_2d2d(wl.mat_a, wl.mat_b, wl.offs, out32)  # noqa: E731
+        else:
+            fn = lambda: mod.grouped_mm(wl.mat_a, wl.mat_b, offs=wl.offs)  # noqa: E731
         ms = time_steps(None, fn, steps, warmup) / steps
         return {"value": wl.flops / (ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms, "steps": steps}
     except Exception as exc:  # the baseline is informative; its failure must not hide our number
@@ -403,6 +491,140 @@ def expert_parallel_leg(dist, dev, rank: int, world: int, tokens: int = 16384, t
     return res
 
 
+# ----------------------------------------------------------------------------- legs beside the headline
+
+
+def roofline_of(wl, ms: float, peaks, sustained: bool = False):
+    """Roofline position of one launch: bound = the slower of FLOPs / tensor peak and bytes / HBM peak."""
+    tflops_peak = peaks["tflops_sustained"] if (sustained and peaks["tflops_sustained"]) else peaks["tflops"]
+    t_flops = wl.flops / (tflops_peak * 1e12) * 1e3
+    t_bytes = wl.algorithmic_bytes / (peaks["hbm_gbs"] * 1e9) * 1e3
+    return {"bound": "tensor" if t_flops >= t_bytes else "hbm", "floor_ms": max(t_flops, t_bytes),
+            "frac": max(t_flops, t_bytes) / ms, "TFLOP/s": wl.flops / (ms * 1e-3) / 1e12,
+            "GB/s": wl.algorithmic_bytes / (ms * 1e-3) / 1e9}
+
+
+def sampled_within_tolerance(wl, out, max_rows: int = 96):
+    """Slab-sampled check of a result against the CPU oracle: rows spread over every group (one per
+    32-row slab, thinned to at most `max_rows`), all columns. Returns the worst error as a fraction
+    of the tolerance |out - ref| <= 8e-3 |ref| + 1e-2 sqrt(K) sigma_a sigma_b (<= 1 passes)."""
+    from oracle.grouped_mm_oracle import atol_for, group_bounds, max_violation  # the checker
+
+    def pick(rows):
+        return rows[:: max(1, -(-len(rows) // max_rows))]
+
+    worst = 0.0
+    if wl.form == "2d3d":
+        bounds = group_bounds(wl.offs.cpu(), wl.mat_a.size(0))
+        rows = pick([(g, r) for g, (s, e) in enumerate(bounds) for r in range(s + 5 % max(1, e - s), e, 32)])
+        atol = atol_for(wl.k, wl.sigma_a, wl.sigma_b)
+        for g in sorted({g for g, _ in rows}):
+            idx = torch.tensor([r for gg, r in rows if gg == g], device=out.device)
+            ref = wl.mat_a[idx].cpu().float() @ wl.mat_b[g].cpu().float()
+            worst = max(worst, max_violation(out[idx], ref, torch.ones_like(ref, dtype=torch.bool), atol))
+    elif wl.form == "3d3d":
+        atol = atol_for(wl.k, wl.sigma_a, wl.sigma_b)
+        per = max(1, max_rows // wl.mat_a.size(0))
+        for g in range(wl.mat_a.size(0)):
+            idx = torch.tensor(pick(list(range(5, wl.mat_a.size(1), 32)))[:per], device=out.device)
+            ref = wl.mat_a[g][idx].cpu().float() @ wl.mat_b[g].cpu().float()
+            worst = max(worst, max_violation(out[g][idx], ref, torch.ones_like(ref, dtype=torch.bool), atol))
+    else:  # 2d2d: every group, a few rows each; empty groups must be exactly zero
+        bounds = group_bounds(wl.offs.cpu(), wl.mat_a.size(1))
+        idx = torch.tensor(pick(list(range(5, wl.mat_a.size(0), 32)))[:8], device=out.device)
+        a_rows, b_cpu = wl.mat_a[idx].cpu().float(), wl.mat_b.cpu().float()
+        for g, (s, e) in enumerate(bounds):
+            if e == s:
+                worst = max(worst, 0.0 if float(out[g].abs().max()) == 0.0 else float("inf"))
+                continue
+            ref = a_rows[:, s:e] @ b_cpu[s:e]
+            worst = max(worst, max_violation(out[g][idx], ref, torch.ones_like(ref, dtype=torch.bool),
+                                             atol_for(e - s, wl.sigma_a, wl.sigma_b)))
+    return float(worst)
+
+
+KERNEL_NAMES = {0: "none", 1: "gmm_sm100_kernel (one CTA per 128x256 tile)", 2: "gmm_generic_kernel",
+                3: "gmm_sm100_pair_kernel (cta_group::2, CTA pair per 256x256 tile)"}
+
+
+def all_configs_leg(dev, peaks, steps: int = 20, with_triton: bool = True):
+    """The other benchmark configurations, each timed for `steps` launches (CUDA events) and checked
+    on a slab sample against the CPU oracle; the reference's Triton kernel beside each where it runs."""
+    from grouped_mm_bf16_b200 import _lib, _op
+
+    forms = {"2d3d": _lib.FORM_2D3D, "3d3d": _lib.FORM_3D3D, "2d2d": _lib.FORM_2D2D, "3d2d": _lib.FORM_3D2D}
+    res = {}
+    for name in ("readme", "batched", "deepseek_up", "deepseek_down", "wgrad"):
+        try:
+            wl = make_workload(name, dev, seed=0)
+            out = call_operator(wl)
+            entry = {"kernel": KERNEL_NAMES.get(_op.selected_kernel(forms[wl.form], wl.mat_a, wl.mat_b, out), "?")}
+            entry["within_tolerance"] = sampled_within_tolerance(wl, out)
+            del out
+            sampler = ClockSampler(dev.index or 0)
+            ms = time_steps(None, lambda: call_operator(wl), steps, 3, sampler) / steps
+            entry.update({"ms": ms, "steps": steps, "flops": wl.flops, "algorithmic_bytes": wl.algorithmic_bytes,
+                          "sm_mhz": sampler.summary()["sm_mhz"], "reasons": sampler.summary()["reasons"]})
+            entry.update(roofline_of(wl, ms, peaks))
+            if name == "readme":
+                entry["note"] = "196608 FLOP: launch latency only, no roofline meaning"
+            if with_triton:
+                entry["triton_reference"] = triton_reference_tflops(wl, 5, 2)
+            entry["device_status"] = _op.check_status(dev)
+            res[name] = entry
+            del wl
+            torch.cuda.empty_cache()
+        except Exception as exc:  # informative legs must not hide the headline number
+            res[name] = {"error": f"{type(exc).__name__}: {exc}"[:200]}
+    return res
+
+
+def sustained_leg(step_fn, flops: float, ms_hint: float, peaks, device_index: int, min_seconds: float = 2.0):
+    """The same launch repeated back to back for at least `min_seconds`: the power-capped steady
+    state, against the sustained cuBLAS peak. ms x MHz separates clock effects from kernel effects."""
+    steps = max(20, int(min_seconds * 1e3 / max(ms_hint, 1e-3)) + 1)
+    sampler = ClockSampler(device_index, period_s=0.02)
+    ms = time_steps(None, step_fn, steps, 3, sampler) / steps
+    clocks = sampler.summary()
+    tf = flops / (ms * 1e-3) / 1e12
+    return {"value": tf, "unit": UNIT, "ms_per_step": ms, "steps": steps, "seconds": ms * steps * 1e-3,
+            "sm_mhz_median": clocks["sm_mhz"], "reasons": clocks["reasons"],
+            "ms_x_mhz": (ms * clocks["sm_mhz"]) if clocks["sm_mhz"] else None,
+            "frac_of_sustained_peak": (tf / peaks["tflops_sustained"]) if peaks["tflops_sustained"] else None,
+            "sustained_peak": peaks["tflops_sustained"]}
+
+
+def cublas_yardstick(dev, peaks, m: int = 32768, k: int = 4096, n: int = 14336):
+    """torch.matmul (cuBLAS) on the dense GEMM of the headline's size, in this process: a yardstick
+    for what the box gives a library kernel at the same moment, as a burst and sustained."""
+    gen = torch.Generator(device=dev).manual_seed(5)
+    a = torch.randn((m, k), device=dev, generator=gen).bfloat16()
+    b = (torch.randn((k, n), device=dev, generator=gen) * 0.02).bfloat16()
+    out = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+    flops = 2.0 * m * k * n
+    fn = lambda: torch.matmul(a, b, out=out)  # noqa: E731
+    sampler = ClockSampler(dev.index or 0)
+    burst_ms = time_steps(None, fn, 20, 5, sampler) / 20
+    res = {"what": f"torch.matmul bf16 [{m},{k}] @ [{k},{n}] (one dense GEMM with the headline's FLOPs)",
+           "burst": {"value": flops / (burst_ms * 1e-3) / 1e12, "unit": UNIT, "ms": burst_ms, "steps": 20,
+                     "sm_mhz_median": sampler.summary()["sm_mhz"]},
+           "sustained": sustained_leg(fn, flops, burst_ms, peaks, dev.index or 0)}
+    return res
+
+
+def copy_rates_leg(dist, dev, nbytes: int = 512 << 20):
+    """Per-direction pinned-host copy rate of every rank, all ranks copying at the same time."""
+    host = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+    devbuf = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    res = {}
+    for name, fn in (("h2d", lambda: devbuf.copy_(host, non_blocking=True)),
+                     ("d2h", lambda: host.copy_(devbuf, non_blocking=True))):
+        ms = time_steps(dist, fn, 4, 1) / 4
+        res[name + "_GBps_per_rank"] = rank_stats(dist, nbytes / (ms * 1e-3) / 1e9)
+    res["what"] = f"{nbytes >> 20} MiB pinned copies, every rank at once, each direction alone"
+    return res
+
+
 # ----------------------------------------------------------------------------- main arm
 
 
@@ -456,6 +678,7 @@ def main():
     sampler = ClockSampler(local)
     ms_total = time_steps(dist, lambda: call_operator(wl), args.steps, args.warmup, sampler)
     status = _op.check_status(dev)
+    per_rank_ms = rank_stats(dist, ms_total / args.steps) if world > 1 else None
     ms_total = max_over_ranks(dist, ms_total)
     ms_step = ms_total / args.steps
     total_flops = sum_over_ranks(dist, wl.flops)
@@ -473,10 +696,13 @@ def main():
         gbs = wl.algorithmic_bytes / (my_ms * 1e-3) / 1e9
         roofline = {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                     "frac": gbs / peaks["hbm_gbs"]}
+    traffic, traffic_note = (None, "not captured for TF32") if args.tf32 else ncu_traffic_bytes(args.workload)
+    if args.dims_scale != 1.0 or args.rows_scale != 1.0:
+        traffic, traffic_note = None, "reduced size"
     roofline.update({
-        "traffic": None if args.tf32 else NCU_TRAFFIC_BYTES.get(args.workload),
-        "peak_source": f"{peaks['source']} (burst cuBLAS bf16 / copy bandwidth)",
-        "frac_of_sustained_peak": (achieved / peaks["tflops_sustained"]) if peaks["tflops_sustained"] else None,
+        "traffic": traffic, "traffic_source": traffic_note,
+        "peak_source": f"{peaks['source']} (burst cuBLAS bf16 / copy bandwidth): the timed region of the default "
+                       "20 steps is a burst; see `sustained` for the power-capped figure against the sustained peak",
         "frac_of_nominal_2250": None if args.tf32 else achieved / 2250.0,
         "algorithmic_flops_per_launch": wl.flops, "algorithmic_bytes_per_launch": wl.algorithmic_bytes,
         "kernel": {1: "gmm_sm100_kernel (TMA + tcgen05.mma, one CTA per 128x256 tile)", 2: "gmm_generic_kernel",
@@ -509,36 +735,57 @@ def main():
                 out_h.copy_(res, non_blocking=True)
 
         e_steps = max(3, min(args.steps, 20))
-        e_ms = max_over_ranks(dist, time_steps(dist, e2e_step, e_steps, 3)) / e_steps
+        e_ms_mine = time_steps(dist, e2e_step, e_steps, 3) / e_steps
+        e_ms = max_over_ranks(dist, e_ms_mine)
         h2d = a_h.numel() * a_h.element_size() + b_h.numel() * b_h.element_size() + \
             (offs_h.numel() * 4 if offs_h is not None else 0)
         d2h = out_h.numel() * out_h.element_size()
+        rates = copy_rates_leg(dist, dev) if world > 1 else None
         e2e = {"value": total_flops / (e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": int(h2d),
                "d2h_bytes_per_step": int(d2h), "ms_per_step": e_ms, "steps": e_steps,
                "api": "grouped_mm_bf16_b200.host.grouped_mm_host (pinned host in/out, copies overlapped with compute)"
                if wl.form == "2d3d" and wl.mat_b.is_contiguous() else "pinned host -> device copies, grouped_mm, copy back"}
+        if rates is not None:
+            e2e["host_copy_rates"] = rates
+            e2e["per_rank_ms"] = rank_stats(dist, e_ms_mine)
         del a_h, b_h, out_h
 
-    # strong split of ONE workload across the ranks (reported beside the weak number)
+    # strong split of ONE workload across the ranks (reported beside the weak number): by rows, cutting
+    # a hot expert across consecutive ranks (each holds a copy of its weights), and by whole experts.
     strong = None
     if world > 1:
         sizes = group_sizes(args.workload, 0)
-        if sizes is not None:
-            lo, hi = partition_groups(sizes, world)[rank]
-            local_sizes = sizes[lo:hi]
-            if sum(local_sizes) > 0:
-                swl = make_workload(args.workload, dev, seed=0, sizes=local_sizes,
-                                    dtype=torch.float32 if args.tf32 else torch.bfloat16)
-                s_ms = time_steps(dist, lambda: call_operator(swl), args.steps, args.warmup)
-                s_flops = swl.flops
-            else:
-                s_ms = time_steps(dist, lambda: None, args.steps, args.warmup)
-                s_flops = 0.0
-            s_ms_max = max_over_ranks(dist, s_ms) / args.steps
+        if sizes is not None and wl.form == "2d3d":
+            def strong_leg(local_sizes):
+                if sum(local_sizes) > 0:
+                    swl = make_workload(args.workload, dev, seed=0, sizes=local_sizes,
+                                        dtype=torch.float32 if args.tf32 else torch.bfloat16)
+                    s_ms = time_steps(dist, lambda: call_operator(swl), args.steps, args.warmup) / args.steps
+                    s_flops = swl.flops
+                else:
+                    s_ms = time_steps(dist, lambda: None, args.steps, args.warmup) / args.steps
+                    s_flops = 0.0
+                return s_ms, s_flops
+
+            pieces = partition_rows(sizes, world)
+            s_ms, s_flops = strong_leg([rows for _, _, rows in pieces[rank]])
             s_total = sum_over_ranks(dist, s_flops)
-            strong = {"value": s_total / (s_ms_max * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": s_ms_max,
-                      "row_balance_mean_over_max": imbalance(sizes, world),
-                      "note": "one 8-expert workload split by contiguous expert ranges, row-balanced"}
+            s_max = max_over_ranks(dist, s_ms)
+            loads = [sum(r for _, _, r in ps) for ps in pieces]
+            strong = {"value": s_total / (s_max * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": s_max,
+                      "per_rank_ms": rank_stats(dist, s_ms),
+                      "row_balance_mean_over_max": (sum(loads) / len(loads)) / max(loads),
+                      "experts_cut": sum(1 for g in range(len(sizes)) if sum(1 for ps in pieces for p in ps if p[0] == g) > 1),
+                      "note": "one 8-expert workload split by rows: rank r owns rows [r T / N, (r+1) T / N); an expert "
+                              "whose rows span several ranks has its weights on each of them, placed before timing"}
+            lo, hi = partition_groups(sizes, world)[rank]
+            w_ms, w_flops = strong_leg(sizes[lo:hi])
+            w_total = sum_over_ranks(dist, w_flops)
+            w_max = max_over_ranks(dist, w_ms)
+            strong["whole_experts"] = {"value": w_total / (w_max * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": w_max,
+                                       "per_rank_ms": rank_stats(dist, w_ms),
+                                       "row_balance_mean_over_max": imbalance(sizes, world),
+                                       "note": "the same workload split by contiguous whole-expert ranges, row-balanced"}
 
     ep_block = None
     if world > 1 and args.ep_block:
@@ -551,17 +798,12 @@ def main():
             "vs_baseline": None,
             "dtype": "fp32 in/out multiplied as TF32, f32 accumulate (NOT the benchmark dtype)" if args.tf32
             else "bf16 in/out, f32 accumulate", "data": "synthetic",
-            "config": {
-                "workload": f"{args.workload}: form {wl.form}, a {tuple(wl.mat_a.shape)}, b {tuple(wl.mat_b.shape)}, "
-                            f"{len(wl.sizes) if wl.sizes else wl.mat_a.size(0)} groups per GPU, seeded sizes",
-                "sharding": "expert-parallel, one process per GPU, no collective in the timed region",
-                "l2": "inputs larger than L2 (no flush needed)",
-                "reduced": None if (args.dims_scale == 1.0 and args.rows_scale == 1.0) else
-                f"NOT the benchmark size: dims x{args.dims_scale}, rows x{args.rows_scale} (profiling case)",
-            },
+            "config": workload_config(args, wl),
             "roofline": roofline, "e2e": e2e, "gpu_launches": args.steps, "clocks": sampler.summary(),
             "device_status": status,
         }
+        if per_rank_ms is not None:
+            line["per_rank_ms"] = per_rank_ms
         if ep_block is not None:
             line["expert_parallel_block"] = ep_block
         if strong is not None:
@@ -573,6 +815,13 @@ def main():
             line["cpu_baseline"] = {"value": f / dt / 1e12, "unit": UNIT, "cores": os.cpu_count() or 1,
                                     "kind": "port", "sample": desc}
             line["triton_reference"] = triton_reference_tflops(wl, max(3, min(args.steps, 20)), 3)
+            try:
+                line["sustained"] = sustained_leg(lambda: call_operator(wl), wl.flops, ms_step, peaks, local)
+                line["cublas_yardstick"] = cublas_yardstick(dev, peaks)
+            except Exception as exc:  # informative legs must not hide the headline number
+                line["sustained_error"] = f"{type(exc).__name__}: {exc}"[:200]
+            if args.workload == "mixtral" and args.dims_scale == 1.0 and args.rows_scale == 1.0 and not args.tf32:
+                line["all_configs"] = all_configs_leg(dev, peaks)
             if wl.form == "2d3d":
                 from grouped_mm_bf16_b200 import grouped_mm
 

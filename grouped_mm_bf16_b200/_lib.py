@@ -40,6 +40,7 @@ EXPORTED_SYMBOLS = (
     "grouped_mm_3d2d",
     "grouped_mm_2d3d_swiglu",
     "grouped_mm_2d3d_static_scratch",
+    "gmm_zero_past_offsets",
     "gmm_select_kernel",
     "gmm_check_status",
     "gmm_selftest_wait_timeout",
@@ -111,6 +112,10 @@ def load() -> ctypes.CDLL:
         lib.grouped_mm_2d3d_static_scratch.restype = ctypes.c_int
         lib.grouped_mm_2d3d_static_scratch.argtypes = [tp, tp, ctypes.c_void_p, ctypes.c_int32, tp, ctypes.c_void_p,
                                                        ctypes.c_uint32, ctypes.POINTER(ctypes.c_void_p)]
+        lib.gmm_zero_past_offsets.restype = ctypes.c_int
+        lib.gmm_zero_past_offsets.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64, ctypes.c_int64,
+                                              ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p, ctypes.c_int32,
+                                              ctypes.c_void_p]
         lib.gmm_select_kernel.restype = ctypes.c_int
         lib.gmm_select_kernel.argtypes = [ctypes.c_int32, tp, tp, tp, ctypes.c_uint32]
         lib.gmm_check_status.restype = ctypes.c_int

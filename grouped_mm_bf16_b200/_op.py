@@ -254,6 +254,42 @@ def grouped_mm_2d3d_swiglu(mat_a: torch.Tensor, gate_up: torch.Tensor, offs: tor
     return True
 
 
+def _zero_past_offsets(t: torch.Tensor, dim: int, offs: torch.Tensor) -> None:
+    lib = _lib.load()
+    if t.dim() != 2 or t.element_size() not in (2, 4):
+        raise RuntimeError("zero_past_offsets takes a 2-D tensor of 2- or 4-byte elements")
+    if t.numel() == 0:
+        return
+    offs = offs.contiguous()
+    other = 1 - dim
+    with torch.cuda.device(t.device):
+        rc = lib.gmm_zero_past_offsets(ctypes.c_void_p(t.data_ptr()), t.element_size(), t.size(dim), t.size(other),
+                                       t.stride(dim), t.stride(other), ctypes.c_void_p(offs.data_ptr()),
+                                       offs.numel(), ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream))
+    if rc != 0:
+        raise RuntimeError(_lib.error_message(lib, rc))
+
+
+@torch.library.custom_op("grouped_mm_b200::zero_past_offsets", mutates_args=("t",), device_types="cuda")
+def _zero_past_offsets_op(t: torch.Tensor, dim: int, offs: torch.Tensor) -> None:
+    _zero_past_offsets(t, dim, offs)
+
+
+@_zero_past_offsets_op.register_fake
+def _(t, dim, offs):
+    return None
+
+
+def zero_past_offsets(t: torch.Tensor, dim: int, offs: torch.Tensor) -> None:
+    """Zero-fills ``t`` (2-D) at indices >= offs[-1] along ``dim``: the part of a ragged output that no
+    group owns and the kernels leave untouched. The offset is read on the device (no host wait), and
+    nothing is written when it equals the extent. A registered custom op under torch.compile."""
+    if torch.compiler.is_compiling():
+        _zero_past_offsets_op(t, dim, offs)
+    else:
+        _zero_past_offsets(t, dim, offs)
+
+
 def selected_kernel(form: int, mat_a: torch.Tensor, mat_b: torch.Tensor, out: torch.Tensor) -> int:
     """Which kernel a call with these tensors is routed to (0 none, 1 tcgen05 single-CTA, 2 generic,
     3 tcgen05 CTA-pair)."""

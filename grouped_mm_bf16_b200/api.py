@@ -201,7 +201,7 @@ def grouped_mm_2d3d_backward(mat_a, mat_b, offs, grad_out, grad_a, grad_b) -> No
     (2D x 2D; empty groups give zeros). Rows past offs[-1] belong to no group: their gradient is zero."""
     g = _grad_operand(grad_out, mat_a)
     if grad_a is not None:
-        grad_a.zero_()
+        _op.zero_past_offsets(grad_a, 0, offs)
         forward_into(g, mat_b.transpose(-2, -1), offs, grad_a)
     if grad_b is not None:
         forward_into(mat_a.transpose(-2, -1), g, offs, grad_b)
@@ -212,10 +212,10 @@ def grouped_mm_2d2d_backward(mat_a, mat_b, offs, grad_out, grad_a, grad_b) -> No
     dB[ks:ke,:] = A[:,ks:ke]^T dC[g] (2D x 3D). Indices past offs[-1] get zero gradient."""
     g = _grad_operand(grad_out, mat_a)
     if grad_a is not None:
-        grad_a.zero_()
+        _op.zero_past_offsets(grad_a, 1, offs)
         forward_into(g, mat_b.transpose(-2, -1), offs, grad_a)
     if grad_b is not None:
-        grad_b.zero_()
+        _op.zero_past_offsets(grad_b, 0, offs)
         forward_into(mat_a.transpose(-2, -1), g, offs, grad_b)
 
 
@@ -228,7 +228,7 @@ def grouped_mm_3d2d_backward(mat_a, mat_b, offs, grad_out, grad_a, grad_b) -> No
     if grad_a is not None:
         forward_into(g, mat_b.transpose(-2, -1), offs, grad_a)
     if grad_b is not None:
-        grad_b.zero_()
+        _op.zero_past_offsets(grad_b, 1, offs)
         forward_into(mat_a.transpose(-2, -1), g, offs, grad_b)
 
 

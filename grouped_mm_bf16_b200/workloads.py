@@ -209,6 +209,39 @@ def partition_groups(sizes: List[int], world: int) -> List[Tuple[int, int]]:
     return ranges
 
 
+def partition_rows(sizes: List[int], world: int) -> List[List[Tuple[int, int, int]]]:
+    """Row-balanced split that may cut a group: rank r gets rows [r * T / world, (r + 1) * T / world) of the
+    T routed rows, as a list of pieces ``(group, first_row_in_group, rows)``.
+
+    Every rank's rows are still one contiguous slice of ``mat_a`` and of the output. A group cut across
+    consecutive ranks has its weights replicated on each of them (placed before any timing), so the
+    ranks stay independent: no collective, no peer access. Loads differ by at most one row.
+    """
+    if world <= 0:
+        raise ValueError("world must be positive")
+    total = sum(sizes)
+    starts, acc = [], 0
+    for sz in sizes:
+        starts.append(acc)
+        acc += sz
+    out: List[List[Tuple[int, int, int]]] = []
+    g = 0
+    for r in range(world):
+        lo, hi = (r * total) // world, ((r + 1) * total) // world
+        pieces = []
+        while g < len(sizes) and starts[g] + sizes[g] <= lo:
+            g += 1
+        h = g
+        while h < len(sizes) and starts[h] < hi:
+            first = max(lo, starts[h])
+            last = min(hi, starts[h] + sizes[h])
+            if last > first:
+                pieces.append((h, first - starts[h], last - first))
+            h += 1
+        out.append(pieces)
+    return out
+
+
 def shard_sizes(sizes: List[int], world: int, rank: int) -> List[int]:
     lo, hi = partition_groups(sizes, world)[rank]
     return list(sizes[lo:hi])

@@ -175,6 +175,18 @@ int grouped_mm_2d3d_static_scratch(const gmm_tensor_t* a, const gmm_tensor_t* b,
                                    void** scratch_address);
 
 /*
+ * Zero-fills the elements of a 2-D tensor whose index along the ragged dimension is at or past
+ * offs[n_groups - 1] (clamped into [0, extent]; everything when n_groups is 0). `extent` and
+ * `stride_ragged` describe the ragged dimension, `other` and `stride_other` the remaining one;
+ * sizes and strides in elements of `elem_bytes` (2 or 4) bytes. The grouped_mm_* calls leave that
+ * part of their output untouched; a gradient needs zeros there. The offset is read on the device
+ * and nothing is written when it equals `extent`. The reference's backward kernels zero these
+ * elements as part of their own stores (grouped_mm_bf16/kernels.py:1093-1390).
+ */
+int gmm_zero_past_offsets(void* data, int32_t elem_bytes, int64_t extent, int64_t other, int64_t stride_ragged,
+                          int64_t stride_other, const int32_t* offs, int32_t n_groups, void* stream);
+
+/*
  * Which kernel the corresponding grouped_mm_* call would use for these arguments (enum
  * gmm_kernel_kind, or a negative gmm_status). `form`: 0 = 3d3d, 1 = 2d3d, 2 = 3d2d, 3 = 2d2d.
  * Launches nothing. No counterpart in the reference, whose kernels take any strides.
