@@ -256,6 +256,8 @@ def grouped_mm_2d3d_swiglu(mat_a: torch.Tensor, gate_up: torch.Tensor, offs: tor
 
 def _zero_past_offsets(t: torch.Tensor, dim: int, offs: torch.Tensor) -> None:
     lib = _lib.load()
+    if not (t.is_cuda and offs.is_cuda):
+        raise RuntimeError("grouped_mm_b200 is GPU-only; CPU tensors are not supported")
     if t.dim() != 2 or t.element_size() not in (2, 4):
         raise RuntimeError("zero_past_offsets takes a 2-D tensor of 2- or 4-byte elements")
     if t.numel() == 0:

@@ -448,6 +448,71 @@ def test_torch_compile_traces_through_the_custom_op():
     assert torch.equal(got, fn(wl.mat_a, wl.mat_b, wl.offs))
 
 
+def test_backward_under_torch_compile():
+    """Forward and backward through torch.compile with the aot_eager backend: AOTAutograd traces the
+    autograd function's backward with fake tensors, so every launch in it has to be a registered
+    custom op (the GEMMs and the zero-fill past offs[-1])."""
+    wl = make_workload("mixtral", DEV, seed=6, scale=1 / 64, dims_scale=1 / 8)
+    offs = wl.offs.clone()
+    offs[-1] -= 5  # the last five rows belong to no group: their gradient must be zero
+
+    a1, b1 = wl.mat_a.clone().requires_grad_(True), wl.mat_b.clone().requires_grad_(True)
+    a2, b2 = wl.mat_a.clone().requires_grad_(True), wl.mat_b.clone().requires_grad_(True)
+    # rows past offs[-1] are left as allocated by the forward pass: keep them out of the loss
+    def masked(a, b):
+        return (grouped_mm(a, b, offs=offs)[: int(offs[-1])].float() ** 2).sum()
+
+    masked(a1, b1).backward()
+    torch.compile(masked, backend="aot_eager")(a2, b2).backward()
+    assert torch.equal(a1.grad, a2.grad) and torch.equal(b1.grad, b2.grad)
+    assert float(a1.grad[int(offs[-1]):].abs().max()) == 0.0
+
+
+def test_zero_past_offsets_entry_point():
+    """gmm_zero_past_offsets zero-fills exactly the part at or past offs[-1], along either dimension,
+    for contiguous and strided tensors, and touches nothing when offs[-1] is the extent."""
+    for dtype in (torch.bfloat16, torch.float32):
+        for dim in (0, 1):
+            for end in (0, 13, 40):
+                base = torch.ones((40, 56), dtype=dtype, device=DEV)
+                t = base[:, :40] if dim == 1 else base[:, :33]
+                offs = torch.tensor([5, end], dtype=torch.int32, device=DEV)
+                _op.zero_past_offsets(t, dim, offs)
+                want = torch.ones_like(base)
+                if dim == 0:
+                    want[end:, :33] = 0
+                else:
+                    want[:, end:40] = 0
+                assert torch.equal(base, want), (dtype, dim, end)
+    tr = torch.ones((24, 16), dtype=torch.bfloat16, device=DEV).t()  # column-major [16, 24]
+    _op.zero_past_offsets(tr, 1, torch.tensor([20], dtype=torch.int32, device=DEV))
+    assert float(tr[:, :20].min()) == 1.0 and float(tr[:, 20:].abs().max()) == 0.0
+
+
+def test_2d2d_without_group_maps_is_refused(built_library):
+    """The K-ragged tensor-core path needs the caller's group_maps buffer; without it the C entry
+    point returns GMM_ERR_WORKSPACE and launches nothing."""
+    wl = make_workload("wgrad", DEV, seed=0, scale=1 / 16, dims_scale=1 / 8)
+    lib = _lib.load()
+    out = torch.zeros((wl.offs.numel(), wl.mat_a.size(0), wl.mat_b.size(1)), dtype=torch.float32, device=DEV)
+    a, b, c = _op._desc(wl.mat_a), _op._desc(wl.mat_b), _op._desc(out)
+    ws = _op.workspace(DEV)
+    launch = _lib.GmmLaunch()
+    launch.stream = torch.cuda.current_stream().cuda_stream
+    launch.workspace, launch.workspace_bytes, launch.flags = ws.data_ptr(), ws.numel() * 4, 0
+    rc = lib.grouped_mm_2d2d(ctypes.byref(a), ctypes.byref(b), ctypes.c_void_p(wl.offs.data_ptr()), wl.offs.numel(),
+                             ctypes.byref(c), ctypes.byref(launch))
+    assert rc == -4
+    need = int(lib.gmm_group_maps_bytes(wl.offs.numel()))
+    assert need == 256 * wl.offs.numel()
+    maps = torch.empty(need, dtype=torch.uint8, device=DEV)
+    launch.group_maps, launch.group_maps_bytes = maps.data_ptr(), need
+    rc = lib.grouped_mm_2d2d(ctypes.byref(a), ctypes.byref(b), ctypes.c_void_p(wl.offs.data_ptr()), wl.offs.numel(),
+                             ctypes.byref(c), ctypes.byref(launch))
+    assert rc == 0
+    assert torch.equal(out, grouped_mm(wl.mat_a, wl.mat_b, offs=wl.offs, out_dtype=torch.float32))
+
+
 def test_side_stream_and_cuda_graph_replay():
     """The call only enqueues work on the current stream (no host sync, no allocation inside the
     library), so it can run on a side stream and be captured into a CUDA graph and replayed."""

@@ -125,6 +125,73 @@ def _rank_main(rank: int, world: int, port: int, out_path: str):
         dist.destroy_process_group()
 
 
+def test_partition_rows_balances_to_one_row_and_cuts_hot_groups():
+    from grouped_mm_bf16_b200.workloads import partition_rows
+
+    for name in ("mixtral", "deepseek_up", "wgrad"):
+        sizes = group_sizes(name, 0)
+        for world in (1, 2, 3, 4, 8):
+            parts = partition_rows(sizes, world)
+            loads = [sum(r for _, _, r in ps) for ps in parts]
+            assert len(parts) == world and sum(loads) == sum(sizes) and max(loads) - min(loads) <= 1
+            # the pieces, in rank order, tile every group exactly once and in order
+            seen = {}
+            last_g = -1
+            for ps in parts:
+                for g, first, rows in ps:
+                    assert rows > 0 and g >= last_g and first == seen.get(g, 0)
+                    seen[g] = first + rows
+                    last_g = g
+            assert all(seen.get(g, 0) == sz for g, sz in enumerate(sizes))
+    # the hot expert of the Mixtral-shape draw (14787 of 32768 rows) is cut over four of eight ranks
+    parts = partition_rows(group_sizes("mixtral", 0), 8)
+    assert sum(1 for ps in parts if any(g == 0 for g, _, _ in ps)) == 4
+    assert partition_rows([0, 5, 0, 3], 3) == [[(1, 0, 2)], [(1, 2, 3)], [(3, 0, 3)]]
+
+
+def _rank_main_rows(rank, world, port, out_path):
+    """Row-split sharding with a group cut across the two ranks: each rank holds a copy of the weights
+    of the groups it touches, computes its rows with the CPU checker standing in for the device
+    kernel, and the gathered rows must equal the unsharded result."""
+    import torch.distributed as dist
+    from grouped_mm_bf16_b200.workloads import partition_rows
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        sizes = [100, 20, 0, 9, 3]  # the first group holds most rows and is cut
+        wl = make_workload("mixtral", "cpu", seed=3, sizes=sizes, dims_scale=1 / 64)
+        pieces = partition_rows(sizes, world)[rank]
+        starts = [sum(sizes[:g]) for g in range(len(sizes))]
+        row0 = starts[pieces[0][0]] + pieces[0][1]
+        local_rows = sum(r for _, _, r in pieces)
+        a_local = wl.mat_a[row0:row0 + local_rows]
+        b_local = wl.mat_b[[g for g, _, _ in pieces]]          # this rank's copies of the weights
+        offs_local = torch.tensor([r for _, _, r in pieces]).cumsum(0).to(torch.int32)
+        part, _ = grouped_mm_oracle(a_local, b_local, offs_local)
+        gathered = [torch.zeros((sum(sizes), part.size(1))) for _ in range(world)]
+        padded = torch.zeros((sum(sizes), part.size(1)))
+        padded[:local_rows] = part
+        dist.all_gather(gathered, padded)
+        counts = [torch.zeros(1, dtype=torch.int64) for _ in range(world)]
+        dist.all_gather(counts, torch.tensor([local_rows]))
+        if rank == 0:
+            full = torch.cat([g[: int(c)] for g, c in zip(gathered, counts)])
+            ref, _ = grouped_mm_oracle(wl.mat_a, wl.mat_b, wl.offs)
+            torch.save(dict(max_err=float((full - ref).abs().max()), rows=int(full.size(0)),
+                            cut=len(pieces) >= 1 and pieces[-1][2] < sizes[pieces[-1][0]]), out_path)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_row_split_with_a_cut_group_over_gloo(tmp_path):
+    out = tmp_path / "result_rows.pt"
+    mp.spawn(_rank_main_rows, args=(2, _free_port(), str(out)), nprocs=2, join=True)
+    res = torch.load(out)
+    assert res["rows"] == 132 and res["max_err"] == 0.0 and res["cut"]
+
+
 def test_two_rank_group_sharding_over_gloo(tmp_path):
     out = tmp_path / "result.pt"
     mp.spawn(_rank_main, args=(2, _free_port(), str(out)), nprocs=2, join=True)

@@ -62,6 +62,17 @@ def test_static_scratch_entry_matches_regular_entry_on_two_calls_in_a_row(built_
         ref, defined = grouped_mm_oracle(a, b, offs)
         assert max_violation(got, ref, defined, atol_for(a.size(1), 1.0, 1.0)) <= 1.0
     assert addresses[0] == addresses[1], "every call on a device shares the one scratch block"
+    # The property the entry point exists for: once its first call on the device has looked up the
+    # array's address, a call takes no device memory, neither from the driver nor from torch's pool.
+    a, b, offs = problems[0]
+    got = torch.empty((a.size(0), b.size(2)), dtype=torch.bfloat16, device=DEV)
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    pool_before, reserved_before = torch.cuda.memory_allocated(), torch.cuda.memory_reserved()
+    _call_static(lib, a, b, offs, got)
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before
+    assert torch.cuda.memory_allocated() == pool_before and torch.cuda.memory_reserved() == reserved_before
 
 
 def test_static_scratch_entry_rejects_what_the_regular_entry_rejects(built_library):
