@@ -82,20 +82,20 @@ int init_device(int dev) {
     if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_kernel<true, float>);
     if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_kernel<false, float, 4>);
     if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_kernel<true, float, 4>);
-    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_pair_kernel<false, float, false, 4>, PairShape<false, float>::SMEM);
-    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_pair_kernel<true, float, false, 4>, PairShape<true, float>::SMEM);
+    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_pair_kernel<false, float, false, 4>, kPairSmemBytes);
+    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_pair_kernel<true, float, false, 4>, kPairSmemBytes);
     if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_kernel<false, __nv_bfloat16, 2, true>);
     if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_kernel<false, __half, 2, true>);
     if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_kernel<false, float, 2, true>);
-    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_pair_kernel<false, __nv_bfloat16, true>, PairShape<false, __nv_bfloat16>::SMEM);
-    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_pair_kernel<false, __half, true>, PairShape<false, __half>::SMEM);
-    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_pair_kernel<false, float, true>, PairShape<false, float>::SMEM);
-    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_pair_kernel<false, __nv_bfloat16>, PairShape<false, __nv_bfloat16>::SMEM);
-    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_pair_kernel<false, __half>, PairShape<false, __half>::SMEM);
-    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_pair_kernel<false, float>, PairShape<false, float>::SMEM);
-    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_pair_kernel<true, __nv_bfloat16>, PairShape<true, __nv_bfloat16>::SMEM);
-    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_pair_kernel<true, __half>, PairShape<true, __half>::SMEM);
-    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_pair_kernel<true, float>, PairShape<true, float>::SMEM);
+    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_pair_kernel<false, __nv_bfloat16, true>, kPairSmemBytes);
+    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_pair_kernel<false, __half, true>, kPairSmemBytes);
+    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_pair_kernel<false, float, true>, kPairSmemBytes);
+    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_pair_kernel<false, __nv_bfloat16>, kPairSmemBytes);
+    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_pair_kernel<false, __half>, kPairSmemBytes);
+    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_pair_kernel<false, float>, kPairSmemBytes);
+    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_pair_kernel<true, __nv_bfloat16>, kPairSmemBytes);
+    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_pair_kernel<true, __half>, kPairSmemBytes);
+    if (rc == GMM_OK) rc = set_smem_attr(gmm_sm100_pair_kernel<true, float>, kPairSmemBytes);
     d.status = rc;
   });
   return d.status;
@@ -377,11 +377,9 @@ template <typename TOut>
 int launch_pair_t(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const FastParams& fp, int grid,
                   cudaStream_t st) {
   if (fp.p.mode == MODE_KRAGGED)
-    gmm_sm100_pair_kernel<true, TOut>
-        <<<grid, PairShape<true, TOut>::THREADS, PairShape<true, TOut>::SMEM, st>>>(ta, tb, tc, fp);
+    gmm_sm100_pair_kernel<true, TOut><<<grid, kFastThreads, kPairSmemBytes, st>>>(ta, tb, tc, fp);
   else
-    gmm_sm100_pair_kernel<false, TOut>
-        <<<grid, PairShape<false, TOut>::THREADS, PairShape<false, TOut>::SMEM, st>>>(ta, tb, tc, fp);
+    gmm_sm100_pair_kernel<false, TOut><<<grid, kFastThreads, kPairSmemBytes, st>>>(ta, tb, tc, fp);
   GMM_CUDA_TRY(cudaGetLastError());
   return GMM_OK;
 }
@@ -402,8 +400,7 @@ template <typename TOut>
 int launch_swiglu_t(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const FastParams& fp, bool pair,
                     int grid, cudaStream_t st) {
   if (pair)
-    gmm_sm100_pair_kernel<false, TOut, true>
-        <<<grid, PairShape<false, TOut>::THREADS, PairShape<false, TOut>::SMEM, st>>>(ta, tb, tc, fp);
+    gmm_sm100_pair_kernel<false, TOut, true><<<grid, kFastThreads, kPairSmemBytes, st>>>(ta, tb, tc, fp);
   else
     gmm_sm100_kernel<false, TOut, 2, true><<<grid, kFastThreads, kFastSmemBytes, st>>>(ta, tb, tc, fp);
   GMM_CUDA_TRY(cudaGetLastError());
@@ -480,11 +477,9 @@ int launch_fast(const CanonProblem& p_in, const FastPlan& plan, const DeviceInfo
   if (tf32) {
     if (plan.pair) {
       if (p.mode == MODE_KRAGGED)
-        gmm_sm100_pair_kernel<true, float, false, 4>
-            <<<grid, PairShape<true, float>::THREADS, PairShape<true, float>::SMEM, st>>>(ta, tb, tc, fp);
+        gmm_sm100_pair_kernel<true, float, false, 4><<<grid, kFastThreads, kPairSmemBytes, st>>>(ta, tb, tc, fp);
       else
-        gmm_sm100_pair_kernel<false, float, false, 4>
-            <<<grid, PairShape<false, float>::THREADS, PairShape<false, float>::SMEM, st>>>(ta, tb, tc, fp);
+        gmm_sm100_pair_kernel<false, float, false, 4><<<grid, kFastThreads, kPairSmemBytes, st>>>(ta, tb, tc, fp);
     } else if (p.mode == MODE_KRAGGED) {
       gmm_sm100_kernel<true, float, 4><<<grid, kFastThreads, kFastSmemBytes, st>>>(ta, tb, tc, fp);
     } else {

@@ -26,7 +26,7 @@ namespace gmm {
 
 constexpr int kPairBM = 256;       // rows of a pair tile (128 per CTA)
 constexpr int kPairBNHalf = 128;   // B columns held by one CTA
-constexpr int kPairStages = 6;      // ring depth (the wide-epilogue variant below uses one less)
+constexpr int kPairStages = 6;
 constexpr int kPairAStageBytes = 128 * kBK * 2;            // 16 KiB
 constexpr int kPairBStageBytes = kPairBNHalf * kBK * 2;    // 16 KiB
 constexpr int kPairStageBytes = kPairAStageBytes + kPairBStageBytes;
@@ -41,20 +41,8 @@ struct PairSmemTail {
   SchedSmem sched;
 };
 
-// Shape of one instantiation. The K-ragged form with a 32-bit result (the weight-gradient call) has
-// short main loops (a tile's K is one group's length, often a few k-blocks) and twice the output
-// bytes per tile, so its epilogue, not its MMAs, sets the pace: it gets eight epilogue warps (two per
-// TMEM lane quarter, each taking 128 of the tile's 256 columns) and pays for their staging areas
-// with one ring stage. Every other instantiation has four epilogue warps and six stages.
-template <bool KRAGGED, typename TOut>
-struct PairShape {
-  static constexpr bool WIDE = KRAGGED && sizeof(TOut) == 4;
-  static constexpr int STAGES = WIDE ? kPairStages - 1 : kPairStages;
-  static constexpr int EPI_WARPS = WIDE ? 8 : 4;
-  static constexpr int THREADS = 64 + 32 * EPI_WARPS;
-  static constexpr size_t SMEM =
-      1024 + size_t(STAGES) * kPairStageBytes + size_t(EPI_WARPS) * kWarpStageBytes + sizeof(PairSmemTail);
-};
+constexpr size_t kPairSmemBytes =
+    1024 + size_t(kPairStages) * kPairStageBytes + kEpilogueStageBytes + sizeof(PairSmemTail);
 
 enum PairStatus : int {
   ST_PAIR_PRODUCER_TIMEOUT = 0x201,
@@ -67,18 +55,15 @@ enum PairStatus : int {
 // gate in columns 0..127 and up in 128..255, and the stored tile is 256 x 128.
 // ES: operand element size, 2 (bf16/fp16) or 4 (fp32 read as TF32), as in the single-CTA kernel.
 template <bool KRAGGED, typename TOut, bool SWIGLU = false, int ES = 2>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__((PairShape<KRAGGED, TOut>::THREADS), 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFastThreads, 1)
 gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                       const __grid_constant__ CUtensorMap tmap_c, const FastParams fp) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  using Shape = PairShape<KRAGGED, TOut>;
-  constexpr int STAGES = Shape::STAGES;
-  constexpr int EPI_WARPS = Shape::EPI_WARPS;
   uint8_t* smem_a = smem;
-  uint8_t* smem_b = smem + STAGES * kPairAStageBytes;
-  uint8_t* epi_stage = smem + STAGES * kPairStageBytes;  // 1024-byte aligned
-  PairSmemTail& tail = *reinterpret_cast<PairSmemTail*>(epi_stage + EPI_WARPS * kWarpStageBytes);
+  uint8_t* smem_b = smem + kPairStages * kPairAStageBytes;
+  uint8_t* epi_stage = smem + kPairStages * kPairStageBytes;  // 1024-byte aligned
+  PairSmemTail& tail = *reinterpret_cast<PairSmemTail*>(epi_stage + kEpilogueStageBytes);
   volatile int* abort_flag = &tail.abort_flag;
 
   using EG = ElemGeom<ES>;
@@ -94,13 +79,13 @@ gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   const int n_pairs = gridDim.x >> 1;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
+    for (int s = 0; s < kPairStages; ++s) {
       mbar_init(&tail.full[s], 1);
       mbar_init(&tail.empty[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tail.acc_full[b], 1);
-      mbar_init(&tail.acc_empty[b], 2 * 32 * EPI_WARPS);
+      mbar_init(&tail.acc_empty[b], 2 * kEpilogueThreads);
     }
     tail.abort_flag = 0;
     fence_barrier_init();
@@ -175,12 +160,12 @@ gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
 #pragma unroll
             for (int c = 0; c < kChunks; ++c) load_b(sb + c * EG::CHUNK_BYTES, col0 + c * EG::CHUNK_W, k);
           }
-          if (++s == STAGES) { s = 0; ph ^= 1; }
+          if (++s == kPairStages) { s = 0; ph ^= 1; }
         }
       }
       // After a give-up: a bounded time for the copies already requested (by either CTA: all are
       // credited to the leader's barriers) to land before the pair leaves.
-      if (!ok && rank == 0) drain_ring<STAGES>(tail.full, s, ph);
+      if (!ok && rank == 0) drain_ring<kPairStages>(tail.full, s, ph);
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (leader CTA, one thread)
@@ -230,17 +215,14 @@ gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                                (kb | k) != 0 ? 1u : 0u);
           }
           umma_commit_pair(&tail.empty[s], 0x3);  // frees the stage in both CTAs
-          if (++s == STAGES) { s = 0; ph ^= 1; }
+          if (++s == kPairStages) { s = 0; ph ^= 1; }
         }
         if (ok) umma_commit_pair(&tail.acc_full[buf], 0x3);
       }
     }
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5 of both CTAs)
-    const int q = warp & 3;                                // TMEM lane quarter this warp may read
-    const int col_half = (warp - 2) >> 2;                  // 0, or 1 for the second set of four warps
-    constexpr int COLS_PER_WARP = BNT / (EPI_WARPS / 4);   // columns of the tile one warp stores
-    static_assert(EPI_WARPS == 4 || !SWIGLU, "the fused activation reads both accumulator halves in one warp");
+    const int q = warp & 3;
     TOut* c_base = reinterpret_cast<TOut*>(p.c);
     int it = 0;
     bool ok = true;
@@ -258,20 +240,19 @@ gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       }
       tcgen05_fence_after_sync();
       const int row0 = int(rank) * 128 + q * 32;  // first row of this warp inside the pair tile
-      const int c0 = col_half * COLS_PER_WARP;  // first column of the tile this warp stores
       TOut* c_warp = c_base + (long long)ti.g * p.c_sg + (long long)(ti.m0 + row0) * p.c_sm +
-                     (long long)(ti.n0 + c0) * p.c_sn;
-      const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + buf * kBN + c0;
-      const int ncols_tile = min(COLS_PER_WARP, p.N - ti.n0 - c0);
-      // A warp whose rows lie wholly past the group's end, or whose columns lie past N, has nothing to do.
-      if (row0 < ti.rows && ncols_tile > 0) {
+                     (long long)ti.n0 * p.c_sn;
+      const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + buf * kBN;
+      const int ncols_tile = min(BNT, p.N - ti.n0);
+      // A warp whose rows lie wholly past the group's end has nothing to read or store.
+      if (row0 < ti.rows) {
         if constexpr (SWIGLU)
           epilogue_store_warp_swiglu<TOut>(t_row, c_warp, p.c_sm, p.c_sn, ti.rows - row0, ncols_tile,
                                            epi_stage + (warp - 2) * kWarpStageBytes, lane);
         else
           epilogue_store_warp<TOut>(t_row, c_warp, p.c_sm, p.c_sn, ti.rows - row0, ncols_tile,
                                     epi_stage + (warp - 2) * kWarpStageBytes, KRAGGED && ti.klen == 0, lane,
-                                    fp.c_tma ? &tmap_c : nullptr, ti.n0 + c0, ti.m0 + row0,
+                                    fp.c_tma ? &tmap_c : nullptr, ti.n0, ti.m0 + row0,
                                     p.mode == MODE_MRAGGED ? 0 : ti.g);
       }
       tcgen05_fence_before_sync();
