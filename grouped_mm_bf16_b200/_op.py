@@ -142,12 +142,70 @@ def _worth_relayout(form: int, mat_a: torch.Tensor, mat_b: torch.Tensor, out: to
     return flops >= RELAYOUT_MIN_FLOPS
 
 
-def _launch(form: int, mat_a: torch.Tensor, mat_b: torch.Tensor, offs: Optional[torch.Tensor], out: torch.Tensor) -> None:
+# ---------------------------------------------------------------------------------------------
+# Splitting the contraction of the K-ragged form.
+#
+# A 2D x 2D call has G * ceil(M / 256) * ceil(N / 256) output tiles, however long the groups are: a
+# weight gradient of small experts (say M = N = 256, 4 groups, tens of thousands of rows each) would
+# keep 4 of the GPU's 74 CTA pairs busy. Such a call is run as G * S groups instead: every group's
+# range [ks, ke) is cut into S consecutive pieces (computed on the device from `offs`, no host
+# wait), the kernel writes the S partial products to an fp32 scratch tensor, and they are added in a
+# fixed order, so results stay run-to-run reproducible. The reference's kernel has the same shortage
+# of parallelism (one program per output tile looping over all of K, kernels.py:248-301).
+
+_SM_COUNT: dict[int, int] = {}
+
+
+def _split_k_factor(mat_a: torch.Tensor, mat_b: torch.Tensor, offs: torch.Tensor) -> int:
+    if os.environ.get("GROUPED_MM_B200_SPLIT_K", "1") == "0":
+        return 1
+    groups, m, k_total, n = offs.numel(), mat_a.size(0), mat_a.size(1), mat_b.size(1)
+    if groups == 0 or m == 0 or n == 0:
+        return 1
+    idx = mat_a.device.index if mat_a.device.index is not None else torch.cuda.current_device()
+    sms = _SM_COUNT.get(idx)
+    if sms is None:
+        sms = _SM_COUNT[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    units = max(1, sms // 2)
+    tiles = groups * (-(-m // 256)) * (-(-n // 256))
+    mean_k = k_total // groups
+    if 2 * tiles > units or mean_k < 2048:
+        return 1
+    return max(1, min(-(-units // tiles), mean_k // 1024, (_lib_max_groups() - 1) // groups, 32))
+
+
+def _lib_max_groups() -> int:
+    return 1024  # the library rejects n_groups >= 1024
+
+
+def _split_offsets(offs: torch.Tensor, k_total: int, splits: int) -> torch.Tensor:
+    """END offsets of the G * S pieces: piece s of group g ends at ks + (ke - ks) * (s + 1) // S."""
+    ends = offs.long().clamp(0, k_total)
+    starts = torch.cat([ends.new_zeros(1), ends[:-1]])
+    lens = (ends - starts).clamp_min(0)
+    steps = torch.arange(1, splits + 1, device=offs.device)
+    return (starts[:, None] + (lens[:, None] * steps) // splits).reshape(-1).to(torch.int32)
+
+
+def _launch(form: int, mat_a: torch.Tensor, mat_b: torch.Tensor, offs: Optional[torch.Tensor], out: torch.Tensor,
+            may_split: bool = True) -> None:
     lib = _lib.load()
     if not (mat_a.is_cuda and mat_b.is_cuda and out.is_cuda):
         raise RuntimeError("grouped_mm_b200 is GPU-only; CPU tensors are not supported")
     if _worth_relayout(form, mat_a, mat_b, out):
         mat_a, mat_b = tensor_core_layouts(form, mat_a, mat_b)
+    if may_split and form == _lib.FORM_2D2D and mat_a.dtype != torch.float32:
+        splits = _split_k_factor(mat_a, mat_b, offs)
+        if splits > 1 and selected_kernel(form, mat_a, mat_b, out) in _lib.TCGEN05_KINDS:
+            groups = offs.numel()
+            partial = torch.empty((groups * splits, out.size(1), out.size(2)), dtype=torch.float32, device=out.device)
+            _launch(form, mat_a, mat_b, _split_offsets(offs, mat_a.size(1), splits), partial, may_split=False)
+            parts = partial.view(groups, splits, out.size(1), out.size(2))
+            if out.dtype == torch.float32 and out.is_contiguous():
+                torch.sum(parts, dim=1, out=out)
+            else:
+                out.copy_(parts.sum(1))
+            return
     if offs is not None:
         offs = offs.contiguous()  # the library reads n_groups consecutive int32 values
     dev = mat_a.device

@@ -21,7 +21,8 @@ import torch
 
 from .api import forward_into, output_geometry
 
-_DEPTH = 3  # device staging slots: one being filled, one being multiplied, one being drained
+_DEPTH = 4    # device staging slots for rows and results: filling, multiplying, draining, and one of slack
+_B_DEPTH = 2  # device staging slots for weights: the ones in use and the ones being uploaded
 
 
 class _Staging:
@@ -31,14 +32,23 @@ class _Staging:
         self.device = device
         self.h2d = torch.cuda.Stream(device)
         self.d2h = torch.cuda.Stream(device)
-        self.bufs: List[Dict[str, Optional[torch.Tensor]]] = [dict(a=None, b=None, c=None) for _ in range(_DEPTH)]
+        self.bufs: List[Dict[str, Optional[torch.Tensor]]] = [dict(a=None, c=None) for _ in range(_DEPTH)]
         self.free_evt: List[Optional[torch.cuda.Event]] = [None] * _DEPTH  # slot reusable after this event
+        self.b_bufs: List[Optional[torch.Tensor]] = [None] * _B_DEPTH
+        self.b_free_evt: List[Optional[torch.cuda.Event]] = [None] * _B_DEPTH  # last GEMM that read the slot
 
     def take(self, slot: int, key: str, numel: int, dtype: torch.dtype) -> torch.Tensor:
         buf = self.bufs[slot][key]
         if buf is None or buf.numel() < numel or buf.dtype != dtype:
             buf = torch.empty(numel, dtype=dtype, device=self.device)
             self.bufs[slot][key] = buf
+        return buf[:numel]
+
+    def take_b(self, slot: int, numel: int, dtype: torch.dtype) -> torch.Tensor:
+        buf = self.b_bufs[slot]
+        if buf is None or buf.numel() < numel or buf.dtype != dtype:
+            buf = torch.empty(numel, dtype=dtype, device=self.device)
+            self.b_bufs[slot] = buf
         return buf[:numel]
 
 
@@ -56,6 +66,36 @@ def _chunks(sizes: List[int], row_bytes: int, group_bytes: int, target_bytes: in
     if lo < len(sizes):
         out.append((lo, len(sizes)))
     return out
+
+
+def plan_items(sizes: List[int], starts: List[int], row_bytes: int, group_bytes: int, chunk_bytes: int):
+    """The work items of one call, in execution order: ``(lo, hi, r0, r1, new_b)`` = groups [lo, hi), rows
+    [r0, r1) of ``mat_a`` / the result, and whether the groups' weights have to be uploaded (False for the
+    second and later row pieces of one tall group, which reuse the weights already on the device).
+
+    ``row_bytes`` counts a row's way up and its result's way down. A group whose rows move more than
+    ``chunk_bytes`` is cut into row pieces, so that its first results start down the link while its later
+    rows are still going up; the other groups are taken in contiguous runs of about ``chunk_bytes``. Tall
+    groups go first, tallest first (the download stream has work from early on), then the runs by falling
+    size, so that the un-overlapped tail, the last item's multiply and download, is the smallest.
+    """
+    piece_rows = max(256, (chunk_bytes // max(1, row_bytes)) // 256 * 256)
+    tall = [g for g, sz in enumerate(sizes) if sz * row_bytes > chunk_bytes and sz > piece_rows]
+    items = []
+    for g in sorted(tall, key=lambda g: -sizes[g]):
+        for r in range(0, sizes[g], piece_rows):
+            items.append((g, g + 1, starts[g] + r, starts[g] + min(sizes[g], r + piece_rows), r == 0))
+    runs, lo = [], 0
+    for g in tall + [len(sizes)]:  # the short groups between two tall ones, in runs of about chunk_bytes
+        if g > lo:
+            for a, b in _chunks(sizes[lo:g], row_bytes, group_bytes, chunk_bytes):
+                if sum(sizes[lo + a:lo + b]) > 0:
+                    runs.append((lo + a, lo + b))
+        lo = g + 1
+    runs.sort(key=lambda c: -sum(sizes[c[0]:c[1]]))
+    for a, b in runs:
+        items.append((a, b, starts[a], max(starts[a], starts[b - 1] + sizes[b - 1]), True))
+    return items
 
 
 def grouped_mm_host(mat_a: torch.Tensor, mat_b: torch.Tensor, offs: torch.Tensor, out: Optional[torch.Tensor] = None,
@@ -89,34 +129,33 @@ def grouped_mm_host(mat_a: torch.Tensor, mat_b: torch.Tensor, offs: torch.Tensor
     _, out_strides = output_geometry((1, k), (1, k, n), 1, es)  # padded leading stride of a device result
     n_pad = out_strides[0]
 
-    chunks = [(lo, hi) for lo, hi in _chunks(sizes, k * es, k * n * es, chunk_bytes) if sum(sizes[lo:hi]) > 0]
-    # Groups are independent, so the chunks may run in any order. Nothing overlaps the first chunk's
-    # upload or the last chunk's download: start with the smallest chunk and end with the second smallest.
-    chunks.sort(key=lambda c: sum(sizes[c[0]:c[1]]))
-    if len(chunks) > 2:
-        chunks = [chunks[0]] + chunks[:1:-1] + [chunks[1]]
-    # END offsets rebased to each chunk's first row, uploaded once.
-    rebased = torch.tensor([ends[g] - starts[lo] for lo, hi in chunks for g in range(lo, hi)], dtype=torch.int32)
-    offs_dev = rebased.pin_memory().to(dev, non_blocking=True) if rebased.numel() else None
+    items = plan_items(sizes, starts, (k + n) * es, k * n * es, chunk_bytes)
+    # END offsets of every item's groups, rebased to the item's first row, uploaded once.
+    rebased: List[int] = []
+    for lo, hi, r0, r1, _ in items:
+        rebased += [min(max(ends[g], r0), r1) - r0 for g in range(lo, hi)]
+    offs_dev = torch.tensor(rebased, dtype=torch.int32).pin_memory().to(dev, non_blocking=True) if rebased else None
     start_evt = torch.cuda.Event()
     start_evt.record(compute)
     st.h2d.wait_event(start_evt)
     st.d2h.wait_event(start_evt)
 
-    cursor = 0
+    cursor, b_slot, b_d = 0, -1, None
     last_d2h = None
-    for i, (lo, hi) in enumerate(chunks):
+    for i, (lo, hi, r0, r1, new_b) in enumerate(items):
         slot = i % _DEPTH
-        r0 = starts[lo]
-        r1 = max(r0, ends[hi - 1])  # offsets that run backwards make empty groups, never a negative extent
         rows, g = r1 - r0, hi - lo
         with torch.cuda.stream(st.h2d):
             if st.free_evt[slot] is not None:
                 st.h2d.wait_event(st.free_evt[slot])  # the slot's previous result has left the device
             a_d = st.take(slot, "a", rows * k, mat_a.dtype).view(rows, k)
-            b_d = st.take(slot, "b", g * k * n, mat_b.dtype).view(g, k, n)
             a_d.copy_(mat_a[r0:r1], non_blocking=True)
-            b_d.copy_(mat_b[lo:hi], non_blocking=True)
+            if new_b:
+                b_slot = (b_slot + 1) % _B_DEPTH
+                if st.b_free_evt[b_slot] is not None:
+                    st.h2d.wait_event(st.b_free_evt[b_slot])  # the last multiply that read these weights is done
+                b_d = st.take_b(b_slot, g * k * n, mat_b.dtype).view(g, k, n)
+                b_d.copy_(mat_b[lo:hi], non_blocking=True)
             loaded = torch.cuda.Event()
             loaded.record(st.h2d)
         compute.wait_event(loaded)
@@ -125,6 +164,7 @@ def grouped_mm_host(mat_a: torch.Tensor, mat_b: torch.Tensor, offs: torch.Tensor
         cursor += g
         done = torch.cuda.Event()
         done.record(compute)
+        st.b_free_evt[b_slot] = done
         with torch.cuda.stream(st.d2h):
             st.d2h.wait_event(done)
             out[r0:r1].copy_(c_d, non_blocking=True)

@@ -160,12 +160,15 @@ int grouped_mm_2d3d_swiglu(const gmm_tensor_t* a, const gmm_tensor_t* b_gate_up,
  * routine. No counterpart in the reference.
  *
  *  - Limit: the scratch is 256 bytes, which covers every problem grouped_mm_2d3d() accepts (the
- *    scratch need does not grow with the problem); a build whose scratch need exceeded the array
- *    would return GMM_ERR_WORKSPACE here. The group limit (n_groups <= 1023) is unchanged.
+ *    scratch need of the row-ragged form does not grow with the problem; the library checks this
+ *    at compile time). The group limit (n_groups <= 1023) is unchanged.
  *  - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
  *    that device current). Make that first call before any stream capture is begun.
- *  - All calls on a device share the one block. Each call clears it on `stream` before launching,
- *    so nothing from an earlier call leaks in; calls that overlap on the GPU (different streams)
+ *  - All calls on a device share the one block, which keeps what the last call left in it. The
+ *    arguments are checked first; a call that is rejected, or has no work, touches nothing. A call
+ *    that launches clears the status word (the only part that must start at zero) on `stream`
+ *    just before its kernel, so a status code that an earlier call left there and nobody read with
+ *    gmm_check_status() is lost at that point. Calls that overlap on the GPU (different streams)
  *    race on the status word and must be avoided or serialised by the caller.
  *  - *scratch_address, when not NULL, receives the block's device address, usable as the
  *    `workspace` argument of gmm_check_status().

@@ -513,6 +513,26 @@ def test_2d2d_without_group_maps_is_refused(built_library):
     assert torch.equal(out, grouped_mm(wl.mat_a, wl.mat_b, offs=wl.offs, out_dtype=torch.float32))
 
 
+def test_2d2d_with_few_output_tiles_splits_the_contraction(monkeypatch):
+    """M = N = 256 and 4 groups give 4 output tiles for 74 CTA pairs: the call is run as 4 x S groups
+    whose fp32 partial products are summed in a fixed order. Checked against the oracle, against the
+    unsplit kernel, and for run-to-run reproducibility; an empty group stays exactly zero."""
+    sizes = [24576, 0, 8200, 16376]
+    gen = torch.Generator(device=DEV).manual_seed(9)
+    a = torch.randn((sum(sizes), 256), device=DEV, generator=gen).bfloat16().t()
+    b = torch.randn((sum(sizes), 256), device=DEV, generator=gen).bfloat16()
+    offs = _offs(sizes)
+    assert _op._split_k_factor(a, b, offs) > 1
+    out = _assert_parity(a, b, offs, 1.0, 1.0, torch.float32, _lib.GMM_KERNEL_TCGEN05)
+    assert float(out[1].abs().max()) == 0.0
+    assert torch.equal(out, grouped_mm(a, b, offs=offs, out_dtype=torch.float32))
+    out_bf16 = _assert_parity(a, b, offs, 1.0, 1.0, None, _lib.GMM_KERNEL_TCGEN05)
+    monkeypatch.setenv("GROUPED_MM_B200_SPLIT_K", "0")
+    unsplit = grouped_mm(a, b, offs=offs, out_dtype=torch.float32)
+    torch.testing.assert_close(out, unsplit, atol=atol_for(24576, 1, 1) * 0.1, rtol=1e-4)
+    assert out_bf16.dtype == torch.bfloat16
+
+
 def test_side_stream_and_cuda_graph_replay():
     """The call only enqueues work on the current stream (no host sync, no allocation inside the
     library), so it can run on a side stream and be captured into a CUDA graph and replayed."""

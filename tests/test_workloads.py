@@ -197,3 +197,32 @@ def test_two_rank_group_sharding_over_gloo(tmp_path):
     mp.spawn(_rank_main, args=(2, _free_port(), str(out)), nprocs=2, join=True)
     res = torch.load(out)
     assert res["rows"] == 256 and res["max_err"] == 0.0
+
+
+def test_host_entry_plan_covers_every_row_once_and_uploads_weights_once():
+    """grouped_mm_host's work items: every row of every non-empty group in exactly one item, a tall
+    group cut into row pieces that upload its weights only with the first piece, tall groups first."""
+    from grouped_mm_bf16_b200.host import plan_items
+
+    for sizes, chunk in ((group_sizes("mixtral", 0), 192 << 20), ([300, 0, 513, 255, 257, 0, 40, 0], 1 << 12),
+                         ([5, 0, 7], 1 << 30), ([0, 0], 1 << 20)):
+        starts = [sum(sizes[:i]) for i in range(len(sizes))]
+        k, n, es = (4096, 14336, 2) if len(sizes) == 8 and max(sizes) > 1000 else (200, 264, 2)
+        items = plan_items(sizes, starts, (k + n) * es, k * n * es, chunk)
+        covered = [0] * (sum(sizes) + 1)
+        uploads = [0] * len(sizes)
+        for lo, hi, r0, r1, new_b in items:
+            assert 0 <= lo < hi <= len(sizes) and r0 < r1
+            assert r0 >= starts[lo] and r1 <= starts[hi - 1] + sizes[hi - 1]
+            if not new_b:
+                assert hi == lo + 1, "only a single tall group is continued"
+            for r in range(r0, r1):
+                covered[r] += 1
+            if new_b:
+                for g in range(lo, hi):
+                    uploads[g] += 1
+        assert covered[:-1] == [1] * sum(sizes)
+        assert all(u == 1 for g, u in enumerate(uploads) if sizes[g] > 0)
+    items = plan_items(group_sizes("mixtral", 0), [0, 14787, 17079, 17633, 17912, 19184, 21224, 22213],
+                       (4096 + 14336) * 2, 4096 * 14336 * 2, 192 << 20)
+    assert items[0][:2] == (0, 1) and items[0][4] and not items[1][4]  # the hot expert first, in pieces
