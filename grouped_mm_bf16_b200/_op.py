@@ -75,7 +75,7 @@ def _flags(dtype: Optional[torch.dtype] = None) -> int:
 # multiple of 16 bytes, ragged dimension made non-contiguous); the copy costs one pass over A and
 # B, the GEMM then runs at tensor-core speed. Values and results are unchanged.
 
-RELAYOUT_MIN_FLOPS = float(os.environ.get("GROUPED_MM_B200_RELAYOUT_MIN_FLOPS", 1 << 31))
+RELAYOUT_MIN_FLOPS = float(os.environ.get("GROUPED_MM_B200_RELAYOUT_MIN_FLOPS", 1.6e9))
 
 
 def _aligned_rows(t: torch.Tensor) -> bool:
