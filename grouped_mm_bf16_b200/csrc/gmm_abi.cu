@@ -456,6 +456,15 @@ int launch_fast(const CanonProblem& p_in, const FastPlan& plan, const DeviceInfo
   fp.b_mn = plan.b_mn;
   fp.c_tma = c_tma ? 1 : 0;
   fp.idesc = make_idesc(p.in_dtype, plan.a_mn, plan.b_mn, plan.pair ? 256 : 128);
+  fp.idesc_half = 0;
+  fp.tmap_a_half = ta;
+  if (!plan.pair && !swiglu && p.mode != MODE_KRAGGED && env_int("GROUPED_MM_B200_HALF_TILES", 1) != 0) {
+    fp.idesc_half = make_idesc(p.in_dtype, plan.a_mn, plan.b_mn, 64);
+    if (!plan.a_mn) {
+      rc = encode_map(&fp.tmap_a_half, p.a, p.in_dtype, false, p.K, p.M, a_batched ? p.G : 1, p.a_sm, p.a_sg, 64);
+      if (rc != GMM_OK) return rc;
+    }
+  }
   fp.maps_a = fp.maps_b = nullptr;
   if (p.mode == MODE_KRAGGED) {
     // Per-group copies of both maps, each ending at its group's end along K, written on the device

@@ -87,6 +87,11 @@ struct FastParams {
   // zeros in the rows that belong to the next group and contributes exactly nothing.
   const CUtensorMap* maps_a;
   const CUtensorMap* maps_b;
+  // Single-CTA kernel, row-ragged and uniform modes: a tile with at most 64 valid rows (the tail of a
+  // group) is multiplied with M = 64 instructions, which read rows 0..63 of the A stage and leave
+  // rows 16 w .. 16 w + 15 in lanes 0..15 of TMEM lane quarter w. 0 = off (every tile M = 128).
+  uint32_t idesc_half;
+  CUtensorMap tmap_a_half;  // K-major A with a 64-row box, for those tiles (unused when A is MN-major)
 };
 
 // Writes the per-group tensor maps of the K-ragged mode: thread g copies both operands' maps and
@@ -354,7 +359,7 @@ __device__ __forceinline__ void epilogue_store_warp_swiglu(uint32_t t_row, TOut*
 template <bool KRAGGED, typename TOut, int ES = 2, bool SWIGLU = false>
 __global__ void __launch_bounds__(kFastThreads, 1)
 gmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 const __grid_constant__ CUtensorMap tmap_c, const FastParams fp) {
+                 const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ FastParams fp) {
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzled tiles must start on 1024-byte boundaries.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -432,17 +437,20 @@ gmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             ok = false;
             break;
           }
-          mbar_arrive_expect_tx(&tail.full[s], kStageBytes);
+          // A tile of at most 64 valid rows is multiplied with M = 64: only those rows are fetched.
+          const bool half = !KRAGGED && !SWIGLU && fp.idesc_half != 0 && ti.rows <= 64;
+          mbar_arrive_expect_tx(&tail.full[s], half ? kStageBytes - kAStageBytes / 2 : kStageBytes);
           const int k = ti.k0 + kb * BK;
           uint8_t* sa = smem_a + s * kAStageBytes;
           uint8_t* sb = smem_b + s * kBStageBytes;
           auto load_a = [&](void* dst, int x, int y) { tma_load_3d(dst, ta, &tail.full[s], x, y, az); };
           auto load_b = [&](void* dst, int x, int y) { tma_load_3d(dst, tb, &tail.full[s], x, y, bz); };
           if (!fp.a_mn) {
-            load_a(sa, k, ti.m0);
+            if (half) tma_load_3d(sa, &fp.tmap_a_half, &tail.full[s], k, ti.m0, az);
+            else load_a(sa, k, ti.m0);
           } else {
-#pragma unroll
-            for (int c = 0; c < kBM / EG::CHUNK_W; ++c)
+            const int chunks = (half ? 64 : kBM) / EG::CHUNK_W;
+            for (int c = 0; c < chunks; ++c)
               load_a(sa + c * EG::CHUNK_BYTES, ti.m0 + c * EG::CHUNK_W, k);
           }
           if constexpr (SWIGLU) {
@@ -494,8 +502,12 @@ gmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       for (; ok; ++it) {
         const int t = tile_of_round<KRAGGED>(it, blockIdx.x, gridDim.x);
         if (t >= total) break;
-        const int klen = tile_klen(p, tail.sched, t);  // the issuer needs no tile coordinates
+        const int klen = tile_klen(p, tail.sched, t);
         const int nkb = (klen + BK - 1) / BK;
+        uint32_t idesc = fp.idesc;
+        if constexpr (!KRAGGED && !SWIGLU) {
+          if (fp.idesc_half != 0 && decode_tile<kBM, BNT>(p, tail.sched, t).rows <= 64) idesc = fp.idesc_half;
+        }
         const int buf = it & 1;
         const uint32_t aph = (it >> 1) & 1;
         if (!mbar_wait(&tail.acc_empty[buf], aph ^ 1, abort_flag)) {
@@ -516,10 +528,10 @@ gmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
           for (int k = 0; k < BK / EG::UMMA_K; ++k) {
             if constexpr (ES == 4)
-              umma_tf32_ss(d_tmem, a_desc + ((k * a_kstep) >> 4), b_desc + ((k * b_kstep) >> 4), fp.idesc,
+              umma_tf32_ss(d_tmem, a_desc + ((k * a_kstep) >> 4), b_desc + ((k * b_kstep) >> 4), idesc,
                            (kb | k) != 0 ? 1u : 0u);
             else
-              umma_f16_ss(d_tmem, a_desc + ((k * a_kstep) >> 4), b_desc + ((k * b_kstep) >> 4), fp.idesc,
+              umma_f16_ss(d_tmem, a_desc + ((k * a_kstep) >> 4), b_desc + ((k * b_kstep) >> 4), idesc,
                           (kb | k) != 0 ? 1u : 0u);
           }
           umma_commit(&tail.empty[s]);  // frees the stage once these MMAs have read it
@@ -557,7 +569,18 @@ gmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       if constexpr (SWIGLU)
         epilogue_store_warp_swiglu<TOut>(t_row, c_warp, p.c_sm, p.c_sn, ti.rows - q * 32, ncols_tile,
                                          epi_stage + (warp - 2) * kWarpStageBytes, lane);
-      else
+      else if (!KRAGGED && fp.idesc_half != 0 && ti.rows <= 64) {
+        // M = 64 tile: this warp's lanes 0..15 hold rows 16 q .. 16 q + 15; stored row by row
+        // through the staging area, never by TMA (the other 16 lanes hold nothing).
+        if (fp.c_tma) {
+          if (lane == 0) tma_store_wait_read();  // an earlier TMA store may still read the staging area
+          __syncwarp();
+        }
+        TOut* c_half = c_base + (long long)ti.g * p.c_sg + (long long)(ti.m0 + q * 16) * p.c_sm +
+                       (long long)ti.n0 * p.c_sn;
+        epilogue_store_warp<TOut>(t_row, c_half, p.c_sm, p.c_sn, min(16, ti.rows - q * 16), ncols_tile,
+                                  epi_stage + (warp - 2) * kWarpStageBytes, false, lane);
+      } else
         epilogue_store_warp<TOut>(t_row, c_warp, p.c_sm, p.c_sn, ti.rows - q * 32, ncols_tile,
                                   epi_stage + (warp - 2) * kWarpStageBytes, zero_tile, lane,
                                   fp.c_tma ? &tmap_c : nullptr, ti.n0, ti.m0 + q * 32,

@@ -57,7 +57,7 @@ enum PairStatus : int {
 template <bool KRAGGED, typename TOut, bool SWIGLU = false, int ES = 2>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFastThreads, 1)
 gmm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                      const __grid_constant__ CUtensorMap tmap_c, const FastParams fp) {
+                      const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ FastParams fp) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* smem_a = smem;

@@ -21,7 +21,7 @@ import torch
 
 from .api import forward_into, output_geometry
 
-_DEPTH = 4    # device staging slots for rows and results: filling, multiplying, draining, and one of slack
+_DEPTH = 5    # device staging slots for rows and results: filling, multiplying, draining, and two of slack
 _B_DEPTH = 2  # device staging slots for weights: the ones in use and the ones being uploaded
 
 
