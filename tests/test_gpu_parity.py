@@ -513,6 +513,33 @@ def test_2d2d_without_group_maps_is_refused(built_library):
     assert torch.equal(out, grouped_mm(wl.mat_a, wl.mat_b, offs=wl.offs, out_dtype=torch.float32))
 
 
+@pytest.mark.parametrize("b_col_major", [False, True])
+def test_tail_tiles_of_at_most_64_rows_as_m64_mma(b_col_major, monkeypatch):
+    """The single-CTA kernel multiplies a tile with at most 64 valid rows with M = 64 instructions
+    (64 fetched rows, another TMEM layout in the epilogue). Group sizes around the 64- and 128-row
+    boundaries, checked against the oracle with the feature on and off, and against each other:
+    the accumulation order per output element is the same, so the bits are."""
+    monkeypatch.setenv("GROUPED_MM_B200_PAIR", "0")
+    sizes = [1, 63, 64, 65, 0, 130, 192, 17, 128, 129 + 64]
+    g = torch.Generator(device=DEV).manual_seed(23)
+    a = torch.randn((sum(sizes) + 5, 200), device=DEV, generator=g).bfloat16()
+    b = torch.randn((len(sizes), 520, 200), device=DEV, generator=g).bfloat16().transpose(-2, -1) if b_col_major \
+        else torch.randn((len(sizes), 200, 520), device=DEV, generator=g).bfloat16()
+    offs = _offs(sizes)
+    outs = {}
+    for flag in ("1", "0"):
+        monkeypatch.setenv("GROUPED_MM_B200_HALF_TILES", flag)
+        outs[flag] = _assert_parity(a, b, offs, 1.0, 1.0, None, _lib.GMM_KERNEL_TCGEN05)
+        out32 = _assert_parity(a, b, offs, 1.0, 1.0, torch.float32, _lib.GMM_KERNEL_TCGEN05)
+        assert out32.dtype == torch.float32
+    assert torch.equal(outs["1"][: sum(sizes)], outs["0"][: sum(sizes)])
+    # uniform (3D x 3D) blocks of 40 rows are half tiles as well
+    a3 = torch.randn((3, 40, 136), device=DEV, generator=g).bfloat16()
+    b3 = torch.randn((3, 136, 264), device=DEV, generator=g).bfloat16()
+    monkeypatch.setenv("GROUPED_MM_B200_HALF_TILES", "1")
+    _assert_parity(a3, b3, None, 1.0, 1.0, None, _lib.GMM_KERNEL_TCGEN05)
+
+
 def test_2d2d_with_few_output_tiles_splits_the_contraction(monkeypatch):
     """M = N = 256 and 4 groups give 4 output tiles for 74 CTA pairs: the call is run as 4 x S groups
     whose fp32 partial products are summed in a fixed order. Checked against the oracle, against the
