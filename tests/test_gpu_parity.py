@@ -582,6 +582,22 @@ def test_side_stream_and_cuda_graph_replay():
     torch.cuda.synchronize()
     assert torch.equal(static_out, grouped_mm(other.mat_a, wl.mat_b, offs=wl.offs))
 
+    # The K-ragged form: its per-group tensor maps are written on the device, by a kernel that is part
+    # of the captured work, from whatever `offs` holds when the graph runs; a replay after `offs`
+    # has been overwritten in place computes the new split.
+    wg = make_workload("wgrad", DEV, seed=0, scale=1 / 16, dims_scale=1 / 8)
+    grouped_mm(wg.mat_a, wg.mat_b, offs=wg.offs, out_dtype=torch.float32)  # outside the capture: one-time set-up
+    static_offs = wg.offs.clone()
+    graph2 = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph2):
+        static_out2 = grouped_mm(wg.mat_a, wg.mat_b, offs=static_offs, out_dtype=torch.float32)
+    other_offs = _offs(list(reversed(wg.sizes)))
+    assert not torch.equal(other_offs, wg.offs)
+    static_offs.copy_(other_offs)
+    graph2.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(static_out2, grouped_mm(wg.mat_a, wg.mat_b, offs=other_offs, out_dtype=torch.float32))
+
 
 # ----------------------------------------------------------------------------- what must not be written
 
