@@ -1,7 +1,7 @@
 """Installs the unmodified reference package under baseline/_ref (git-ignored; it travels to the GPU
 box with a snapshot of the tree) and puts the reference's own test file beside it.
 
-    python baseline/install_reference.py [/path/to/reference/checkout]
+    python baseline/install_reference.py /path/to/reference/checkout
 
 The install is the offline pip command (pure Python, so --no-deps suffices); the test file is copied
 verbatim to baseline/_ref/tests/ so that it can be run, unchanged, against this repository's
@@ -22,7 +22,9 @@ TARGET = HERE / "_ref"
 
 
 def main() -> None:
-    src = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference").resolve()
+    if len(sys.argv) != 2:
+        raise SystemExit(__doc__)
+    src = Path(sys.argv[1]).resolve()
     if not (src / "grouped_mm_bf16" / "api.py").exists():
         raise SystemExit(f"{src} is not a checkout of the reference")
     with tempfile.TemporaryDirectory() as tmp:
