@@ -251,7 +251,7 @@ FastPlan plan_fast(const CanonProblem& p, uint32_t flags, bool swiglu = false) {
   // The group sizes live on the device, so the host decides on the mean rows per group.
   if (p.N > kPairBNHalf || swiglu) {
     const long long mean_rows = (p.mode == MODE_MRAGGED) ? (long long)p.M / (p.G > 0 ? p.G : 1) : p.M;
-    f.pair = mean_rows >= 768;
+    f.pair = mean_rows >= 512;
     if (flags & GMM_FLAG_FORCE_PAIR) f.pair = true;
     if (flags & GMM_FLAG_NO_PAIR) f.pair = false;
     const int env = env_int("GROUPED_MM_B200_PAIR", -1);  // tuning knob: 0 / 1 overrides the heuristic
