@@ -45,3 +45,39 @@ def test_reference_arm_prints_one_json_line_with_the_contract_keys():
     assert line["impl"] == "reference" and line["unit"] == "TFLOP/s" and line["value"] > 0
     assert line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["cores"] >= 1
     assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["e2e"]["d2h_bytes_per_step"] == 0
+
+
+def test_sampled_tolerance_check_passes_the_oracle_and_catches_a_wrong_tile():
+    """bench.py's slab-sampled checker (used for the `all_configs` key) on CPU tensors: the oracle's own
+    result is within tolerance, a result with one corrupted 32-row slab is not, and a non-zero entry in
+    an empty K-ragged group is reported as infinitely wrong."""
+    from grouped_mm_bf16_b200.workloads import make_workload
+    from oracle.grouped_mm_oracle import grouped_mm_oracle
+
+    wl = make_workload("mixtral", "cpu", seed=0, scale=1 / 64, dims_scale=1 / 32)
+    ref, _ = grouped_mm_oracle(wl.mat_a, wl.mat_b, wl.offs)
+    assert bench.sampled_within_tolerance(wl, ref.bfloat16(), max_rows=10 ** 6) <= 1.0
+    bad = ref.clone()
+    bad[64:96] += 1.0
+    assert bench.sampled_within_tolerance(wl, bad.bfloat16(), max_rows=10 ** 6) > 1.0
+
+    wg = make_workload("wgrad", "cpu", seed=0, scale=1 / 64, dims_scale=1 / 32)
+    ref, _ = grouped_mm_oracle(wg.mat_a, wg.mat_b, wg.offs)
+    assert bench.sampled_within_tolerance(wg, ref) <= 1.0
+    empty = [g for g, s in enumerate(wg.sizes) if s == 0]
+    if empty:
+        ref[empty[0], 3, 3] = 1e-3
+        assert bench.sampled_within_tolerance(wg, ref) == float("inf")
+
+    bt = make_workload("batched", "cpu", seed=0, dims_scale=1 / 32)
+    ref, _ = grouped_mm_oracle(bt.mat_a, bt.mat_b)
+    assert bench.sampled_within_tolerance(bt, ref.bfloat16()) <= 1.0
+
+
+def test_split_offsets_cut_every_group_into_consecutive_pieces():
+    from grouped_mm_bf16_b200 import _op
+
+    offs = torch.tensor([10, 10, 50, 120], dtype=torch.int32)  # the second group is empty, the last is clamped to 100
+    pieces = _op._split_offsets(offs, 100, 4).tolist()
+    assert pieces == [2, 5, 7, 10, 10, 10, 10, 10, 20, 30, 40, 50, 62, 75, 87, 100]
+    assert pieces == sorted(pieces) and pieces[3::4] == [10, 10, 50, 100]
