@@ -599,6 +599,27 @@ def test_side_stream_and_cuda_graph_replay():
     assert torch.equal(static_out2, grouped_mm(wg.mat_a, wg.mat_b, offs=other_offs, out_dtype=torch.float32))
 
 
+def test_k_ragged_calls_on_two_streams_do_not_share_their_group_maps():
+    """Every 2D x 2D call takes its own scratch for the per-group tensor maps from torch's stream-aware
+    allocator, so calls in flight on different streams, with different offsets, do not disturb each
+    other (a shared buffer would let one call's map-building kernel overwrite maps the other's GEMM
+    is still loading through)."""
+    wg = make_workload("wgrad", DEV, seed=0, scale=1 / 4, dims_scale=1 / 4)
+    offs_a, offs_b = wg.offs, _offs(list(reversed(wg.sizes)))
+    want_a = grouped_mm(wg.mat_a, wg.mat_b, offs=offs_a, out_dtype=torch.float32)
+    want_b = grouped_mm(wg.mat_a, wg.mat_b, offs=offs_b, out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    got_a, got_b = [], []
+    for _ in range(6):
+        with torch.cuda.stream(s1):
+            got_a.append(grouped_mm(wg.mat_a, wg.mat_b, offs=offs_a, out_dtype=torch.float32))
+        with torch.cuda.stream(s2):
+            got_b.append(grouped_mm(wg.mat_a, wg.mat_b, offs=offs_b, out_dtype=torch.float32))
+    torch.cuda.synchronize()
+    assert all(torch.equal(g, want_a) for g in got_a) and all(torch.equal(g, want_b) for g in got_b)
+
+
 # ----------------------------------------------------------------------------- what must not be written
 
 
